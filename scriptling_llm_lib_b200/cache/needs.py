@@ -28,6 +28,11 @@ class CacheNeed:
     kv_heads: int
     head_dim: int
     window: int | None = None
+    v_dim: int | None = None      # width of a value head where it differs from the keys' (None: head_dim)
+
+    @property
+    def value_dim(self) -> int:
+        return self.head_dim if self.v_dim is None else self.v_dim
 
     def __post_init__(self):
         if self.kind not in CACHE_KINDS:
@@ -45,6 +50,9 @@ register_cache_kind("window", lambda need, length: length - need.window + 1)
 
 @dataclass(frozen=True)
 class StateNeed:
-    """Per-sequence state of fixed size (a recurrent mixer's carry): zeroed when a slot is opened."""
+    """Per-sequence state of fixed size (a recurrent mixer's carry): zeroed when a slot is opened.
+    A part with several such tensors (a recurrence's carry and the last inputs of its short
+    convolutions) answers `state_need()` with a dict name -> StateNeed; the unit's state is then a
+    dict of tensors under the same names."""
     shape: tuple[int, ...]
     dtype: torch.dtype = torch.float32

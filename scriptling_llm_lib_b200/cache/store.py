@@ -87,8 +87,9 @@ class SequenceCache:
         for need, units in by_need.items():
             # one page more than the pool hands out: padded rows of a replayed decode step write there
             shape = (len(units), n_pages + 1, need.kv_heads, PAGE, need.head_dim)
+            v_shape = shape[:-1] + (need.value_dim,)
             g = KVGroup(need, units, FreeList(n_pages, f"cache page ({need.kind})"),
-                        torch.empty(shape, dtype=dtype, device=device), torch.empty(shape, dtype=dtype, device=device))
+                        torch.empty(shape, dtype=dtype, device=device), torch.empty(v_shape, dtype=dtype, device=device))
             for u in units:
                 self.group_of_unit[u] = len(self.groups)
             self.groups.append(g)
@@ -97,9 +98,11 @@ class SequenceCache:
         # from it and advances it; `length` above and the generation loop's bookkeeping are its host mirror.
         # One spare row serves the padding rows of replayed decode steps.
         self.seq_state = torch.zeros((n_slots + 1, SEQ_STATE_WORDS), dtype=torch.int32, device=device)
-        self.state: dict[int, torch.Tensor] = {
-            unit: torch.zeros((n_slots + 1, *need.shape), dtype=need.dtype, device=device)   # last: spare, for padding
-            for unit, need in state_needs.items() if need is not None}
+        def make(need):                                 # last row: spare, for padding
+            if isinstance(need, dict):
+                return {name: make(n) for name, n in need.items()}
+            return torch.zeros((n_slots + 1, *need.shape), dtype=need.dtype, device=device)
+        self.state: dict[int, torch.Tensor | dict] = {unit: make(need) for unit, need in state_needs.items() if need is not None}
 
     # ------------------------------------------------------------------ slots
     def open(self) -> int:
@@ -107,8 +110,13 @@ class SequenceCache:
         self.length[slot] = 0
         for g in self.groups:
             g.pages[slot] = []
-        for st in self.state.values():
-            st[slot].zero_()
+        def zero(st):
+            if isinstance(st, dict):
+                for t in st.values():
+                    zero(t)
+            else:
+                st[slot].zero_()
+        zero(self.state)
         self.seq_state[slot].zero_()
         return slot
 

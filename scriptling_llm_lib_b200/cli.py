@@ -72,11 +72,11 @@ def main(argv=None) -> int:
     if args.random:
         import torch
         from . import models  # noqa: F401
-        from .config.registry import architecture_for
+        from .config.registry import architecture_for, architecture_name
         from .engine.model import DecoderModel
         from .weights.random_init import write_random_model
         raw = json.loads(open(args.random).read())
-        arch = architecture_for(raw["architectures"][0])
+        arch = architecture_for(architecture_name(raw, args.random))
         cfg = arch.config_class.from_dict(raw, args.random)
         write_random_model(cfg, DecoderModel(arch.layout(cfg)).tensor_specs(), args.seed_weights, args.model, torch.bfloat16)
     prompts = _ids(args.prompt)

@@ -40,11 +40,20 @@ def architecture_for(name: str) -> Architecture:
                           f"{', '.join(registered_architectures()) or '(none)'}") from None
 
 
+def architecture_name(raw: dict, where: str = "config.json") -> str:
+    """The name a config.json chooses its model by: `architectures[0]` (a list of class names), or
+    `architecture` (one string) in folders that write it that way."""
+    archs = raw.get("architectures")
+    if isinstance(archs, list) and archs and isinstance(archs[0], str):
+        return archs[0]
+    one = raw.get("architecture")
+    if isinstance(one, str) and one:
+        return one
+    raise ConfigError(f"{where}: 'architectures' must be a list that names the model class (or 'architecture' a string)")
+
+
 def load_config(model_dir):
     """config.json of `model_dir` -> (Architecture, typed config)."""
     raw, where = read_config_json(model_dir)
-    archs = raw.get("architectures")
-    if not (isinstance(archs, list) and archs and isinstance(archs[0], str)):
-        raise ConfigError(f"{where}: 'architectures' must be a list that names the model class")
-    arch = architecture_for(archs[0])
+    arch = architecture_for(architecture_name(raw, where))
     return arch, arch.config_class.from_dict(raw, where)

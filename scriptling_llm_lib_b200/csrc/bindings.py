@@ -125,7 +125,9 @@ class KernelSet:
         if w.shape[1] != K or tuple(out.shape[-2:]) != (M, N) or (out.dim() == 3 and out.dtype != torch.float32):
             raise KernelError(f"gemm_nt shapes: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)} {out.dtype}")
         out_f32 = 1 if (out.dtype == torch.float32 and self.dtype != torch.float32) else 0
-        _check(self._fn("gemm_nt")(_ptr(a, self.dtype, "a"), _ptr(w, self.dtype, "w"),
+        if a.dtype != self.dtype or not a.is_cuda or a.stride(1) != 1:
+            raise KernelError(f"gemm_nt: a must be {self.dtype} on a CUDA device with unit column stride")
+        _check(self._fn("gemm_nt")(c_void_p(a.data_ptr()), _ptr(w, self.dtype, "w"),
                                    _ptr(out, torch.float32 if out_f32 else self.dtype, "out"), c_int(M), c_int(N),
                                    c_int(K), c_int(a.stride(0)), c_int(w.stride(0)), c_int(N), c_int(out_f32),
                                    c_int(ksplit), _stream()), "gemm_nt")
@@ -218,6 +220,13 @@ class KernelSet:
         if getattr(self, "_fa_tc", None) is None:
             self._fa_tc = PrefillAttentionTC()
         return self._fa_tc
+
+    @property
+    def seq(self) -> "SequenceKernels":
+        """The kernels of mixers with state along the sequence, for this set's element type."""
+        if getattr(self, "_seq", None) is None:
+            self._seq = SequenceKernels(self.dtype)
+        return self._seq
 
     @property
     def decode(self) -> "DecodeKernels":
@@ -540,6 +549,141 @@ class DecodeKernels:
             if tickets.numel() < n_seqs * n_kv:
                 raise KernelError(f"attn_decode tickets hold {tickets.numel()} ints, needs {n_seqs * n_kv}")
             _check(self.lib.sllm_attn_decode_merged_bf16(*head, _ptr(tickets, torch.int32, "tickets"), *tail), "attn_decode")
+
+
+class SequenceKernels:
+    """Launchers of sequence_kernels.cuh: the norm with weighted addends, the short causal convolution
+    with state, the cache write with value norm, attention with values wider or narrower than keys,
+    the gated delta rule and the gated linear recurrence. `dtype` is the element type of activations
+    and weights; state, sums and gates are float32 in both sets."""
+    MAX_ADDENDS = 16
+
+    def __init__(self, dtype: torch.dtype):
+        if dtype not in _SUFFIX:
+            raise KernelError(f"no kernels for {dtype}; supported: float32, bfloat16")
+        self.dtype, self.suffix = dtype, _SUFFIX[dtype]
+        self.lib = load_library("seq_" + self.suffix)
+        self._fns: dict[str, object] = {}
+
+    def _fn(self, name):
+        fn = self._fns.get(name)
+        if fn is None:
+            fn = getattr(self.lib, f"sllm_{name}_{self.suffix}")
+            fn.restype = c_int
+            self._fns[name] = fn
+        return fn
+
+    def _flag(self, t, name):
+        """1 for a float32 buffer, 0 for one of the element type."""
+        if t.dtype == torch.float32:
+            return 1
+        if t.dtype != self.dtype:
+            raise KernelError(f"{name} has dtype {t.dtype}; expected float32 or {self.dtype}")
+        return 0
+
+    @staticmethod
+    def _view(t, name):
+        """Pointer of a [rows, columns] buffer whose rows may be strided (a column slice)."""
+        if not t.is_cuda or t.dim() != 2 or t.stride(1) != 1:
+            raise KernelError(f"{name} must be a CUDA tensor [rows, columns] with unit column stride")
+        return c_void_p(t.data_ptr())
+
+    def add_norm(self, x, addends, rows, weight, y, eps, center):
+        """x float32 [T, d] += sum coef * addend (when rows is None); y [n, d] (float32 or element type) the
+        norm of the (chosen) rows: (v - mean) / sqrt(var + eps) * w if `center`, else v / sqrt(mean v^2 + eps) * w.
+        `addends`: list of (tensor [T, d] float32 or element type, coefficient)."""
+        d = x.shape[-1]
+        if len(addends) > self.MAX_ADDENDS:
+            raise KernelError(f"add_norm takes at most {self.MAX_ADDENDS} addends, got {len(addends)}")
+        for t, _ in addends:
+            if tuple(t.shape) != tuple(x.shape) or not t.is_contiguous():
+                raise KernelError(f"addend {tuple(t.shape)} does not fit the stream {tuple(x.shape)}")
+        n = len(addends)
+        ptrs = (c_void_p * max(1, n))(*[t.data_ptr() for t, _ in addends])
+        coefs = (c_float * max(1, n))(*[float(c) for _, c in addends])
+        flags = (c_int * max(1, n))(*[self._flag(t, "addend") for t, _ in addends])
+        _check(self._fn("add_norm")(_ptr(x, torch.float32, "x"), ptrs, coefs, flags, c_int(n), _ptr(rows, torch.int32, "rows"),
+                                    _ptr(weight, None, "weight"), c_int(self._flag(weight, "weight")),
+                                    _ptr(y, None, "y"), c_int(self._flag(y, "y")), c_int(y.shape[0]), c_int(d), c_float(eps),
+                                    c_int(1 if center else 0), _stream()), "add_norm")
+
+    def causal_conv(self, x, weight, state, ctx, y, taps, in_bias=None, out_bias=None, add_input=False, act=None, y2=None):
+        """y[t] = act(sum_j weight[:, j] * in(t - taps + 1 + j) + out_bias (+ in(t))), in = x + in_bias, over the
+        rows of each sequence of the step; rows before the step come from `state` float32 [slots, taps - 1, C],
+        which afterwards holds the sequence's last taps - 1 inputs. x, y: [T, C] views, float32 or element type."""
+        T, C = x.shape
+        if tuple(weight.shape) != (C, taps) or tuple(y.shape) != (T, C) or (taps > 1 and tuple(state.shape[1:]) != (taps - 1, C)):
+            raise KernelError(f"causal_conv shapes: x {tuple(x.shape)}, weight {tuple(weight.shape)}, y {tuple(y.shape)}")
+        b_f32 = 0
+        for b in (in_bias, out_bias):
+            if b is not None:
+                b_f32 = self._flag(b, "bias")
+        _check(self._fn("causal_conv")(
+            self._view(x, "x"), c_int(self._flag(x, "x")), c_int(x.stride(0)), _ptr(weight, None, "weight"),
+            c_int(self._flag(weight, "weight")), _ptr(in_bias, None, "in_bias"), _ptr(out_bias, None, "out_bias"), c_int(b_f32),
+            _ptr(state, torch.float32, "state") if taps > 1 else c_void_p(0), _ptr(ctx.seq_start, torch.int32, "seq_start"),
+            _ptr(ctx.tok_seq, torch.int32, "tok_seq"), _ptr(ctx.slots, torch.int32, "slots"), self._view(y, "y"),
+            c_int(self._flag(y, "y")), c_int(y.stride(0)), self._view(y2, "y2") if y2 is not None else c_void_p(0),
+            c_int(y2.stride(0) if y2 is not None else 0), c_int(T), c_int(ctx.n_seqs), c_int(C), c_int(taps),
+            c_int(1 if add_input else 0), c_int({None: 0, "silu": 1}[act]), _stream()), "causal_conv")
+
+    def kv_store(self, qkv, tok_pos, tok_seq, block_table, cos_sin, kpages, vpages, n_heads, n_kv, head_dim, v_dim, rot,
+                 interleaved, v_eps):
+        """Rotate queries (in place) and keys by the table, store keys and values (divided by their root
+        mean square when v_eps is not None) at the rows' places in the cache pages."""
+        T, ld = qkv.shape
+        _check(self._fn("kv_store")(_ptr(qkv, self.dtype, "qkv"), c_int(ld), _ptr(tok_pos, torch.int32, "tok_pos"),
+                                    _ptr(tok_seq, torch.int32, "tok_seq"), _ptr(block_table, torch.int32, "block_table"),
+                                    c_int(block_table.shape[1]), _ptr(cos_sin, torch.float32, "cos_sin"),
+                                    _ptr(kpages, self.dtype if kpages is not None else None, "kpages"),
+                                    _ptr(vpages, self.dtype if vpages is not None else None, "vpages"), c_int(T), c_int(n_heads),
+                                    c_int(n_kv), c_int(head_dim), c_int(v_dim), c_int(rot), c_int(1 if interleaved else 0),
+                                    c_float(-1.0 if v_eps is None else v_eps), _stream()), "kv_store")
+
+    def attn_wide_value(self, q, out, tok_pos, tok_seq, block_table, kpages, vpages, n_heads, n_kv, head_dim, v_dim, window, scale):
+        _check(self._fn("attn_wide_value")(_ptr(q, self.dtype, "q"), c_int(q.shape[1]), _ptr(out, self.dtype, "out"),
+                                           c_int(out.shape[1]), _ptr(tok_pos, torch.int32, "tok_pos"),
+                                           _ptr(tok_seq, torch.int32, "tok_seq"), _ptr(block_table, torch.int32, "block_table"),
+                                           c_int(block_table.shape[1]), _ptr(kpages, self.dtype, "kpages"),
+                                           _ptr(vpages, self.dtype, "vpages"), c_int(q.shape[0]), c_int(n_heads), c_int(n_kv),
+                                           c_int(head_dim), c_int(v_dim), c_int(window or 0), c_float(scale), _stream()),
+               "attn_wide_value")
+
+    def delta_prepare(self, qk, ba, a_log, dt_bias, bd, n_heads, n_kv, dk):
+        _check(self._fn("delta_prepare")(self._view(qk, "qk"), c_int(qk.stride(0)), self._view(ba, "ba"), c_int(ba.stride(0)),
+                                         _ptr(a_log, None, "a_log"), _ptr(dt_bias, None, "dt_bias"),
+                                         c_int(self._flag(a_log, "a_log")), _ptr(bd, torch.float32, "bd"), c_int(qk.shape[0]),
+                                         c_int(n_heads), c_int(n_kv), c_int(dk), _stream()), "delta_prepare")
+
+    def delta_rule(self, qk, v, bd, state, ctx, o, n_heads, n_kv, dk, dv):
+        """qk float32 rows [G dk queries | G dk keys] (unit vectors), v float32 [T, H dv], bd float32 [T, 2H]
+        (beta | decay), state float32 [slots, H, dk, dv] (read and advanced), o float32 [T, H dv]."""
+        if qk.dtype != torch.float32 or v.dtype != torch.float32 or tuple(state.shape[1:]) != (n_heads, dk, dv):
+            raise KernelError("delta_rule works on float32 queries, keys, values and state [slots, heads, dk, dv]")
+        _check(self._fn("delta_rule")(self._view(qk, "qk"), c_int(qk.stride(0)), self._view(v, "v"), c_int(v.stride(0)),
+                                      _ptr(bd, torch.float32, "bd"), _ptr(state, torch.float32, "state"),
+                                      _ptr(ctx.seq_start, torch.int32, "seq_start"), _ptr(ctx.slots, torch.int32, "slots"),
+                                      _ptr(o, torch.float32, "o"), c_int(ctx.n_seqs), c_int(n_heads), c_int(n_kv), c_int(dk),
+                                      c_int(dv), _stream()), "delta_rule")
+
+    def gated_unit_rms(self, o, gate, weight, y, n_heads, dv, eps):
+        _check(self._fn("gated_unit_rms")(_ptr(o, torch.float32, "o"), self._view(gate, "gate"), c_int(gate.stride(0)),
+                                          _ptr(weight, None, "weight"), c_int(self._flag(weight, "weight")),
+                                          _ptr(y, self.dtype, "y"), c_int(o.shape[0]), c_int(n_heads), c_int(dv), c_float(eps),
+                                          _stream()), "gated_unit_rms")
+
+    def rglru_scan(self, gates, u, yraw, ra_b, ri_b, lam, y_b, state, ctx, out, block_size):
+        """gates float32 [blocks, T, 2 * block_size], u float32 [T, W], yraw [T, W] view of the element type,
+        state float32 [slots, W] (read and advanced), out [T, W] of the element type."""
+        T, W = u.shape
+        if gates.dtype != torch.float32 or tuple(gates.shape) != (W // block_size, T, 2 * block_size) or yraw.dtype != self.dtype:
+            raise KernelError(f"rglru_scan shapes: gates {tuple(gates.shape)} {gates.dtype}, u {tuple(u.shape)}")
+        _check(self._fn("rglru_scan")(_ptr(gates, torch.float32, "gates"), _ptr(u, torch.float32, "u"), self._view(yraw, "yraw"),
+                                      c_int(yraw.stride(0)), _ptr(ra_b, None, "ra_b"), _ptr(ri_b, None, "ri_b"),
+                                      _ptr(lam, None, "lam"), _ptr(y_b, None, "y_b"), c_int(self._flag(lam, "lam")),
+                                      _ptr(state, torch.float32, "state"), _ptr(ctx.seq_start, torch.int32, "seq_start"),
+                                      _ptr(ctx.slots, torch.int32, "slots"), _ptr(out, self.dtype, "out"), c_int(T),
+                                      c_int(ctx.n_seqs), c_int(W), c_int(block_size), _stream()), "rglru_scan")
 
 
 class CastKernels:

@@ -1,0 +1,390 @@
+// Kernels of the mixers that carry state along a sequence, and of what stands around them: a norm
+// that takes several weighted addends and may subtract the mean, a short causal convolution over
+// time with its last inputs kept per sequence, the gated delta rule, a gated linear recurrence with
+// block-diagonal gates, and attention whose keys and values have different widths.
+//
+// All of them work on the packed rows of a step (seq_start[b] .. seq_start[b + 1] are the rows of
+// sequence b, in order of position) and find a sequence's state through slots[b]. What the state
+// holds is float32 whatever the element type A of activations and weights; every sum, norm, gate,
+// decay and softmax here is float32 too. A buffer whose precision depends on its place in the model
+// (a projection's output in A, a norm's output in float) is passed as void* with a flag.
+#pragma once
+#include "common.cuh"
+
+template <typename A> __device__ __forceinline__ float ld_flag(const void* p, int is_f32, size_t i) {
+  return is_f32 ? ((const float*)p)[i] : to_f32(((const A*)p)[i]);
+}
+template <typename A> __device__ __forceinline__ void st_flag(void* p, int is_f32, size_t i, float v) {
+  if (is_f32) ((float*)p)[i] = v;
+  else ((A*)p)[i] = from_f32<A>(v);
+}
+__device__ __forceinline__ float sigmoid_f(float z) { return 1.0f / (1.0f + expf(-z)); }
+__device__ __forceinline__ float silu_f(float z) { return z / (1.0f + expf(-z)); }
+__device__ __forceinline__ float softplus_f(float z) { return z > 20.0f ? z : log1pf(expf(z)); }
+__device__ __forceinline__ float gelu_tanh_f(float z) {
+  return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
+
+// ------------------------------------------------------------------ residual sum + norm
+// v = x[row] + sum_a coef[a] * addend[a][row]; center: y = (v - mean) / sqrt(var + eps) * w with var the mean of
+// the squared deviations; else y = v / sqrt(mean(v^2) + eps) * w. rows == nullptr: x is updated in place.
+#define SEQ_MAX_ADDENDS 16
+struct SeqAddends {
+  const void* p[SEQ_MAX_ADDENDS];
+  float coef[SEQ_MAX_ADDENDS];
+  int is_f32[SEQ_MAX_ADDENDS];
+  int n;
+};
+
+template <typename A>
+__global__ void add_norm_kernel(float* __restrict__ x, SeqAddends ad, const int* __restrict__ rows,
+                                const void* __restrict__ w, int w_f32, void* __restrict__ y, int y_f32, int d, float eps,
+                                int center) {
+  extern __shared__ float sm_row[];
+  __shared__ float red[32];
+  int r = blockIdx.x;
+  size_t in = rows ? (size_t)rows[r] : (size_t)r;
+  float* xr = x + in * d;
+  bool update = rows == nullptr && ad.n > 0;
+  float s = 0.f;
+  for (int j = threadIdx.x; j < d; j += blockDim.x) {
+    float v = xr[j];
+    for (int a = 0; a < ad.n; a++) v += ad.coef[a] * ld_flag<A>(ad.p[a], ad.is_f32[a], in * d + j);
+    sm_row[j] = v;
+    if (update) xr[j] = v;
+    s += v;
+  }
+  float mean = 0.f;
+  if (center) mean = block_sum(s, red) / (float)d;
+  float ss = 0.f;
+  for (int j = threadIdx.x; j < d; j += blockDim.x) {
+    float c = sm_row[j] - mean;
+    ss += c * c;
+  }
+  ss = block_sum(ss, red);
+  float inv = 1.0f / sqrtf(ss / (float)d + eps);
+  for (int j = threadIdx.x; j < d; j += blockDim.x)
+    st_flag<A>(y, y_f32, (size_t)r * d + j, ((sm_row[j] - mean) * inv) * load_w(w, w_f32, j));
+}
+
+// ------------------------------------------------------------------ short causal convolution over time
+// in(t)[c] = x[t][c] + in_bias[c]; y[t][c] = sum_j w[c][j] * in(t - taps + 1 + j)[c] + out_bias[c] (+ in(t)[c] when
+// add_input), then the activation (0 none, 1 silu). Inputs before the step's first row come from the
+// sequence's state [slot][taps - 1][C] (oldest first; zero for a new sequence). y2 (or null): the same
+// values once more in the element type.
+struct ConvArgs {
+  const void* x; int x_f32; int ldx;
+  const void* w; int w_f32;
+  const void* in_bias; const void* out_bias; int b_f32;
+  float* state;
+  const int* seq_start; const int* tok_seq; const int* slots;
+  void* y; int y_f32; int ldy;
+  void* y2; int ldy2;
+  int C, taps, add_input, act;
+};
+
+template <typename A>
+__global__ void causal_conv_kernel(ConvArgs p) {
+  int t = blockIdx.x;
+  int c = blockIdx.y * blockDim.x + threadIdx.x;
+  if (c >= p.C) return;
+  int b = p.tok_seq[t];
+  int first = p.seq_start[b];
+  int hist = p.taps - 1;
+  const float* st = p.state + (size_t)p.slots[b] * hist * p.C;
+  float ib = p.in_bias ? load_w(p.in_bias, p.b_f32, c) : 0.f;
+  float acc = 0.f, cur = 0.f;
+  for (int j = 0; j < p.taps; j++) {
+    int s = t - hist + j;                       // the row this tap reads
+    float v;
+    if (s >= first) v = ld_flag<A>(p.x, p.x_f32, (size_t)s * p.ldx + c) + ib;
+    else v = st[(size_t)(hist + (s - first)) * p.C + c];      // s - first in [-hist, -1]
+    acc += load_w(p.w, p.w_f32, (size_t)c * p.taps + j) * v;
+    cur = v;
+  }
+  if (p.out_bias) acc += load_w(p.out_bias, p.b_f32, c);
+  if (p.add_input) acc += cur;
+  if (p.act == 1) acc = silu_f(acc);
+  st_flag<A>(p.y, p.y_f32, (size_t)t * p.ldy + c, acc);
+  if (p.y2) ((A*)p.y2)[(size_t)t * p.ldy2 + c] = from_f32<A>(acc);
+}
+
+// After the convolution of a step: the state becomes the last taps - 1 inputs of [state | step's rows].
+template <typename A>
+__global__ void conv_state_update_kernel(ConvArgs p, int n_seqs) {
+  int b = blockIdx.x;
+  int c = blockIdx.y * blockDim.x + threadIdx.x;
+  if (c >= p.C || b >= n_seqs) return;
+  int first = p.seq_start[b], n = p.seq_start[b + 1] - first;
+  int hist = p.taps - 1;
+  float* st = p.state + (size_t)p.slots[b] * hist * p.C;
+  float ib = p.in_bias ? load_w(p.in_bias, p.b_f32, c) : 0.f;
+  for (int k = 0; k < hist; k++) {              // ascending: a kept entry moves down before its place is written
+    int s = n + k - hist;                       // row of the step, or (negative) an entry of the old state
+    float v = s >= 0 ? ld_flag<A>(p.x, p.x_f32, (size_t)(first + s) * p.ldx + c) + ib : st[(size_t)(hist + s) * p.C + c];
+    st[(size_t)k * p.C + c] = v;
+  }
+}
+
+// ------------------------------------------------------------------ positions, value norm, cache write
+// Row t of qkv holds [H query heads of hd | G key heads of hd | G value heads of vd]. The first `rot` dims of
+// every query and key head are turned by the token's position (table cs[pos][i] = (cos, sin)); queries are
+// rewritten in place, keys go to the token's place in the paged cache. Values are divided by their root mean
+// square over vd (v_eps >= 0; v_eps < 0: stored as they are) and stored beside them. G == 0: queries only.
+template <typename A>
+__global__ void kv_store_kernel(A* __restrict__ qkv, int ld, const int* __restrict__ tok_pos, const int* __restrict__ tok_seq,
+                                const int* __restrict__ block_table, int max_pages, const float2* __restrict__ cs,
+                                A* __restrict__ kpages, A* __restrict__ vpages, int H, int G, int hd, int vd, int rot,
+                                int interleaved, float v_eps) {
+  int t = blockIdx.x;
+  int pos = tok_pos[t];
+  int half = rot >> 1;
+  A* row = qkv + (size_t)t * ld;
+  size_t page_slot = 0;
+  if (G > 0) {
+    int page = block_table[(size_t)tok_seq[t] * max_pages + pos / SLLM_PAGE];
+    page_slot = (size_t)page * G * SLLM_PAGE + (pos % SLLM_PAGE);       // + g * PAGE, times the head width
+  }
+  const float2* csr = cs + (size_t)pos * half;
+  for (int idx = threadIdx.x; idx < (H + G) * half; idx += blockDim.x) {
+    int head = idx / half, i = idx % half;
+    int i0 = interleaved ? 2 * i : i, i1 = interleaved ? 2 * i + 1 : i + half;
+    A* h = row + (size_t)head * hd;
+    float x0 = to_f32(h[i0]), x1 = to_f32(h[i1]);
+    float2 c = csr[i];
+    float r0 = x0 * c.x - x1 * c.y, r1 = x1 * c.x + x0 * c.y;
+    if (head < H) {
+      h[i0] = from_f32<A>(r0);
+      h[i1] = from_f32<A>(r1);
+    } else {
+      A* dst = kpages + (page_slot + (size_t)(head - H) * SLLM_PAGE) * hd;
+      dst[i0] = from_f32<A>(r0);
+      dst[i1] = from_f32<A>(r1);
+    }
+  }
+  if (G == 0) return;
+  int tail = hd - rot;
+  for (int idx = threadIdx.x; idx < G * tail; idx += blockDim.x) {
+    int g = idx / tail, j = rot + idx % tail;
+    kpages[(page_slot + (size_t)g * SLLM_PAGE) * hd + j] = row[(size_t)(H + g) * hd + j];
+  }
+  // values: a warp per head
+  int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  const A* vrow = row + (size_t)(H + G) * hd;
+  for (int g = wid; g < G; g += nw) {
+    float scale = 1.f;
+    if (v_eps >= 0.f) {
+      float ss = 0.f;
+      for (int j = lane; j < vd; j += 32) {
+        float v = to_f32(vrow[(size_t)g * vd + j]);
+        ss += v * v;
+      }
+      ss = warp_sum(ss);
+      scale = 1.0f / sqrtf(ss / (float)vd + v_eps);
+    }
+    A* dst = vpages + (page_slot + (size_t)g * SLLM_PAGE) * vd;
+    for (int j = lane; j < vd; j += 32) dst[j] = from_f32<A>(to_f32(vrow[(size_t)g * vd + j]) * scale);
+  }
+}
+
+// ------------------------------------------------------------------ attention, keys of width hd, values of width vd
+// One block of four warps per (row, query head). A warp takes every fourth visible key: the score is a sum
+// over the lanes, the softmax runs on line (a running maximum and sum per warp), and each lane keeps vd / 32
+// sums of weighted values; the four warps are merged at the end. Row t sees the keys at positions
+// max(0, pos - window + 1) .. pos of its own sequence (window 0: all of them).
+template <typename A, int NV>
+__global__ void __launch_bounds__(128) attn_wide_value_kernel(const A* __restrict__ q, int q_ld, A* __restrict__ out, int out_ld,
+                                                              const int* __restrict__ tok_pos, const int* __restrict__ tok_seq,
+                                                              const int* __restrict__ block_table, int max_pages,
+                                                              const A* __restrict__ kpages, const A* __restrict__ vpages, int H,
+                                                              int G, int hd, int vd, int window, float scale) {
+  extern __shared__ float sm_att[];             // q[hd], then per warp: acc[32 * NV], m, l
+  int t = blockIdx.x, h = blockIdx.y;
+  int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  int g = h / (H / G);
+  int pos = tok_pos[t];
+  const int* pages = block_table + (size_t)tok_seq[t] * max_pages;
+  float* qs = sm_att;
+  for (int j = threadIdx.x; j < hd; j += blockDim.x) qs[j] = to_f32(q[(size_t)t * q_ld + (size_t)h * hd + j]);
+  __syncthreads();
+  int lo = window > 0 ? max(0, pos - window + 1) : 0;
+  float m = -INFINITY, l = 0.f, acc[NV];
+#pragma unroll
+  for (int i = 0; i < NV; i++) acc[i] = 0.f;
+  for (int kp = lo + wid; kp <= pos; kp += 4) {
+    size_t at = ((size_t)pages[kp / SLLM_PAGE] * G + g) * SLLM_PAGE + (kp % SLLM_PAGE);
+    const A* kr = kpages + at * hd;
+    float s = 0.f;
+    for (int j = lane; j < hd; j += 32) s += qs[j] * to_f32(kr[j]);
+    s = warp_sum(s) * scale;
+    float m_new = fmaxf(m, s);
+    float c = expf(m - m_new), e = expf(s - m_new);       // expf(-inf) = 0 on the first key
+    l = l * c + e;
+    const A* vr = vpages + at * vd;
+#pragma unroll
+    for (int i = 0; i < NV; i++) {
+      int j = lane + 32 * i;
+      float v = j < vd ? to_f32(vr[j]) : 0.f;
+      acc[i] = acc[i] * c + e * v;
+    }
+    m = m_new;
+  }
+  float* wacc = sm_att + hd + (size_t)wid * (32 * NV + 2);
+#pragma unroll
+  for (int i = 0; i < NV; i++) wacc[lane + 32 * i] = acc[i];
+  if (lane == 0) { wacc[32 * NV] = m; wacc[32 * NV + 1] = l; }
+  __syncthreads();
+  if (wid == 0) {
+    float M = -INFINITY;
+    for (int w = 0; w < 4; w++) M = fmaxf(M, sm_att[hd + (size_t)w * (32 * NV + 2) + 32 * NV]);
+    float L = 0.f;
+    float o[NV];
+#pragma unroll
+    for (int i = 0; i < NV; i++) o[i] = 0.f;
+    for (int w = 0; w < 4; w++) {                         // fixed order
+      const float* wa = sm_att + hd + (size_t)w * (32 * NV + 2);
+      float mw = wa[32 * NV];
+      if (mw == -INFINITY) continue;
+      float c = expf(mw - M);
+      L += wa[32 * NV + 1] * c;
+#pragma unroll
+      for (int i = 0; i < NV; i++) o[i] += wa[lane + 32 * i] * c;
+    }
+    float inv = 1.0f / L;
+#pragma unroll
+    for (int i = 0; i < NV; i++) {
+      int j = lane + 32 * i;
+      if (j < vd) out[(size_t)t * out_ld + (size_t)h * vd + j] = from_f32<A>(o[i] * inv);
+    }
+  }
+}
+
+// ------------------------------------------------------------------ gated delta rule
+// Before the recurrence, per row: queries and keys (float, [G heads of dk] each, at qk and qk + G * dk of a row
+// of ld_qk floats) become unit vectors x / sqrt(sum x^2 + 1e-6), queries times dk^-1/2; ba holds the raw
+// projections [H betas | H decays] of a row (ld_ba floats): beta = sigmoid(b), decay = exp(-exp(A_log) *
+// softplus(a + dt_bias)), written to bd[t][0..H) and bd[t][H..2H).
+template <typename A>
+__global__ void delta_prepare_kernel(float* __restrict__ qk, int ld_qk, const float* __restrict__ ba, int ld_ba,
+                                     const void* __restrict__ a_log, const void* __restrict__ dt_bias, int w_f32,
+                                     float* __restrict__ bd, int H, int G, int dk) {
+  int t = blockIdx.x;
+  int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  float qmult = rsqrtf((float)dk);
+  for (int hh = wid; hh < 2 * G; hh += nw) {
+    float* v = qk + (size_t)t * ld_qk + (size_t)hh * dk;
+    float ss = 0.f;
+    for (int j = lane; j < dk; j += 32) ss += v[j] * v[j];
+    ss = warp_sum(ss);
+    float inv = 1.0f / sqrtf(ss + 1e-6f);
+    if (hh < G) inv *= qmult;
+    for (int j = lane; j < dk; j += 32) v[j] *= inv;
+  }
+  for (int h = threadIdx.x; h < H; h += blockDim.x) {
+    const float* r = ba + (size_t)t * ld_ba;
+    bd[(size_t)t * 2 * H + h] = sigmoid_f(r[h]);
+    float dt = softplus_f(r[H + h] + load_w(dt_bias, w_f32, h));
+    bd[(size_t)t * 2 * H + H + h] = expf(-expf(load_w(a_log, w_f32, h)) * dt);
+  }
+}
+
+// The recurrence itself. One warp per (32 value columns, head, sequence); a lane owns one column j of the
+// head's state S [dk][dv] (row-major in the state tensor [slot][H][dk][dv]) in registers and walks the
+// sequence's rows in order: S *= decay; u = beta * (v_j - sum_d S[d] k[d]); S[d] += k[d] u; o_j = sum_d S[d] q[d].
+// q and k of a row are staged in shared memory by the warp. DK >= dk is the register array's length.
+template <int DK>
+__global__ void __launch_bounds__(32) delta_rule_kernel(const float* __restrict__ qk, int ld_qk, const float* __restrict__ v,
+                                                         int ld_v, const float* __restrict__ bd, float* __restrict__ state,
+                                                         const int* __restrict__ seq_start, const int* __restrict__ slots,
+                                                         float* __restrict__ o, int H, int G, int dk, int dv) {
+  __shared__ float sq[DK], sk[DK];
+  int lane = threadIdx.x;
+  int j = blockIdx.x * 32 + lane, h = blockIdx.y, b = blockIdx.z;
+  int g = h / (H / G);
+  bool live = j < dv;
+  float* Sg = state + (((size_t)slots[b] * H + h) * dk) * dv + j;
+  float S[DK];
+#pragma unroll
+  for (int d = 0; d < DK; d++) S[d] = (live && d < dk) ? Sg[(size_t)d * dv] : 0.f;
+  for (int d = dk + lane; d < DK; d += 32) { sq[d] = 0.f; sk[d] = 0.f; }
+  int t0 = seq_start[b], t1 = seq_start[b + 1];
+  for (int t = t0; t < t1; t++) {
+    __syncwarp();
+    const float* qr = qk + (size_t)t * ld_qk + (size_t)g * dk;
+    const float* kr = qr + (size_t)G * dk;
+    for (int d = lane; d < dk; d += 32) { sq[d] = qr[d]; sk[d] = kr[d]; }
+    float beta = bd[(size_t)t * 2 * H + h], decay = bd[(size_t)t * 2 * H + H + h];
+    float vj = live ? v[(size_t)t * ld_v + (size_t)h * dv + j] : 0.f;
+    __syncwarp();
+    float dot = 0.f;
+#pragma unroll
+    for (int d = 0; d < DK; d++) {
+      S[d] *= decay;
+      dot += S[d] * sk[d];
+    }
+    float u = beta * (vj - dot);
+    float oj = 0.f;
+#pragma unroll
+    for (int d = 0; d < DK; d++) {
+      S[d] += sk[d] * u;
+      oj += S[d] * sq[d];
+    }
+    if (live) o[(size_t)t * H * dv + (size_t)h * dv + j] = oj;
+  }
+  if (live) {
+#pragma unroll
+    for (int d = 0; d < DK; d++)
+      if (d < dk) Sg[(size_t)d * dv] = S[d];
+  }
+}
+
+// Read-out: y[t][h][:] = o / sqrt(mean(o^2) + eps) * w[:] * silu(gate[t][h][:]); a warp per (row, head).
+template <typename A>
+__global__ void gated_unit_rms_kernel(const float* __restrict__ o, const A* __restrict__ gate, int ld_gate,
+                                      const void* __restrict__ w, int w_f32, A* __restrict__ y, int T, int H, int dv, float eps) {
+  int lane = threadIdx.x & 31;
+  size_t idx = (size_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (idx >= (size_t)T * H) return;
+  size_t t = idx / H, h = idx % H;
+  const float* orow = o + (t * H + h) * dv;
+  float ss = 0.f;
+  for (int j = lane; j < dv; j += 32) ss += orow[j] * orow[j];
+  ss = warp_sum(ss);
+  float inv = 1.0f / sqrtf(ss / (float)dv + eps);
+  for (int j = lane; j < dv; j += 32) {
+    float gt = silu_f(to_f32(gate[t * ld_gate + h * dv + j]));
+    y[(t * H + h) * dv + j] = from_f32<A>(orow[j] * inv * load_w(w, w_f32, j) * gt);
+  }
+}
+
+// ------------------------------------------------------------------ real-gated linear recurrence
+// Channel c of width W lies in block c / bs of the gates; gates[block][t][0..bs) is the raw recurrence gate,
+// [bs..2bs) the raw input gate (block-diagonal products of u, float). r = sigmoid(. + ra_b), i = sigmoid(. + ri_b),
+// a = exp(-8 r softplus(lam)); S = a S + sqrt(1 - a^2) i u from the sequence's state [slot][W];
+// out[t][c] = S * gelu_tanh(yraw[t][c] + y_b[c]). A thread per (sequence, channel).
+template <typename A>
+__global__ void rglru_scan_kernel(const float* __restrict__ gates, const float* __restrict__ u, const A* __restrict__ yraw,
+                                  int ld_y, const void* __restrict__ ra_b, const void* __restrict__ ri_b,
+                                  const void* __restrict__ lam, const void* __restrict__ y_b, int w_f32,
+                                  float* __restrict__ state, const int* __restrict__ seq_start, const int* __restrict__ slots,
+                                  A* __restrict__ out, int T, int W, int bs) {
+  int b = blockIdx.x;
+  int c = blockIdx.y * blockDim.x + threadIdx.x;
+  if (c >= W) return;
+  int blk = c / bs, cc = c % bs;
+  float sp = softplus_f(load_w(lam, w_f32, c));
+  float rb = load_w(ra_b, w_f32, c), ib = load_w(ri_b, w_f32, c), yb = load_w(y_b, w_f32, c);
+  float* sp_state = state + (size_t)slots[b] * W + c;
+  float S = *sp_state;
+  const float* gb = gates + (size_t)blk * T * 2 * bs;
+  int t0 = seq_start[b], t1 = seq_start[b + 1];
+  for (int t = t0; t < t1; t++) {
+    float r = sigmoid_f(gb[(size_t)t * 2 * bs + cc] + rb);
+    float i = sigmoid_f(gb[(size_t)t * 2 * bs + bs + cc] + ib);
+    float log_a = -8.0f * r * sp;
+    float a = expf(log_a);
+    S = a * S + sqrtf(-expm1f(2.0f * log_a)) * (i * u[(size_t)t * W + c]);      // 1 - a^2 without cancellation
+    out[(size_t)t * W + c] = from_f32<A>(S * gelu_tanh_f(to_f32(yraw[(size_t)t * ld_y + c]) + yb));
+  }
+  *sp_state = S;
+}

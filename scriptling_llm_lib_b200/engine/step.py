@@ -15,7 +15,7 @@ import numpy as np
 import torch
 
 from ..cache import PAGE, SequenceCache, pages_for
-from ..config.registry import architecture_for, load_config
+from ..config.registry import architecture_for, architecture_name, load_config
 from ..csrc.bindings import CastKernels, KernelSet
 from ..weights.loader import load_weights, stored_to_kept
 from .graphs import DecodeGraphs
@@ -155,7 +155,7 @@ class Engine:
     def bytes_per_page(self) -> int:
         """Device bytes one page of PAGE tokens costs over all cache units."""
         width = torch.empty((), dtype=self.dtype).element_size()
-        return sum(2 * len(units) * need.kv_heads * PAGE * need.head_dim * width
+        return sum(len(units) * need.kv_heads * PAGE * (need.head_dim + need.value_dim) * width
                    for need, units in ((g.need, g.units) for g in self.cache.groups))
 
     # ------------------------------------------------------------------ construction
@@ -174,8 +174,7 @@ class Engine:
             spec = parse_random_spec(model_dir)
             with open(spec.config_path) as f:
                 raw = json.load(f)
-            archs = raw.get("architectures") or [None]
-            arch = architecture_for(archs[0])
+            arch = architecture_for(architecture_name(raw, spec.config_path))
             cfg = arch.config_class.from_dict(raw, spec.config_path)
             layout = arch.layout(cfg)
             specs = DecoderModel(layout).tensor_specs()

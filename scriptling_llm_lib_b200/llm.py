@@ -110,14 +110,14 @@ def random_model(config, seed: int, out_dir, dtype: str = "bfloat16"):
     from pathlib import Path
     import torch
     from . import models  # noqa: F401  (registers the architectures)
-    from .config.registry import architecture_for
+    from .config.registry import architecture_for, architecture_name
     from .engine.model import DecoderModel
     from .weights.random_init import write_random_model
     where = "config"
     if not isinstance(config, dict):
         where = str(config)
         config = json.loads(Path(config).read_text())
-    arch = architecture_for(config["architectures"][0] if config.get("architectures") else None)
+    arch = architecture_for(architecture_name(config, where))
     cfg = arch.config_class.from_dict(config, where)
     specs = DecoderModel(arch.layout(cfg)).tensor_specs()
     return write_random_model(cfg, specs, int(seed), Path(out_dir), {"bfloat16": torch.bfloat16, "float32": torch.float32}[dtype])

@@ -1,1 +1,2 @@
 from . import llama  # noqa: F401  (registers LlamaForCausalLM)
+from . import sozilix  # noqa: F401  (registers Sozilix)

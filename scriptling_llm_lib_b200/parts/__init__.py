@@ -1,4 +1,4 @@
-from . import attention, block, embedding, feedforward, norm, rotary  # noqa: F401  (registers the built-in parts)
+from . import attention, block, delta_rule, embedding, feedforward, norm, parallel, rglru, rotary  # noqa: F401  (registers the built-in parts)
 from .base import (ARRANGEMENTS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, POSITION_ENCODINGS, Embedding, FeedForward,
                    Head, Mixer, Norm, Part, PartSpec, PositionEncoding)
 from .block import Block, LayerSpec, build_block, pre_norm_layer

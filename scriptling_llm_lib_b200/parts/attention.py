@@ -6,6 +6,12 @@ after the query are masked; max-subtracted softmax; out = sum p v; y = out Wo^T
 (model_f32.go:391-470, float32_ops.go:190-235, :252-260). A `window` (absent in the reference)
 also masks keys `window` or more positions behind the query and lets the cache give old pages
 back. With `writes=False` the layer projects queries only and reads the unit another layer wrote.
+Two more options, both absent in the reference: value heads of a width of their own (`v_dim`; the
+cache then keeps values that wide and the output product reads n_heads * v_dim columns), and
+`value_norm_eps`: every value head is divided by its root mean square, sqrt(mean(v^2) + eps),
+before it is cached. Either sends the step's keys and values through a store kernel that does
+rotation, value norm and cache write in one pass (`kv_store`); values as wide as keys then still
+use the attention kernels below, other widths a kernel that takes both (`attn_wide_value`).
 
 The position encoding is optional (`position=None`: queries and keys as projected). Storing keys
 and values in the cache is this mixer's own step, whatever the encoding: for an encoding that is a
@@ -34,17 +40,21 @@ class Attention(Mixer):
 
     def __init__(self, hidden: int, n_heads: int, n_kv_heads: int, head_dim: int, position: PartSpec | None,
                  q_name: str, k_name: str, v_name: str, o_name: str, window: int | None = None,
-                 scale: float | None = None):
+                 scale: float | None = None, v_dim: int | None = None, value_norm_eps: float | None = None):
         if n_heads % n_kv_heads:
             raise ValueError(f"{n_heads} heads cannot share {n_kv_heads} key/value heads")
-        if head_dim % 16:
-            raise ValueError(f"head_dim {head_dim}: the attention kernels take head widths in steps of 16")
+        if not 1 <= head_dim <= 512:
+            raise ValueError(f"head_dim {head_dim}: the attention kernels take head widths 1..512")
         self.hidden, self.n_heads, self.n_kv_heads, self.head_dim, self.window = hidden, n_heads, n_kv_heads, head_dim, window
+        self.v_dim = head_dim if v_dim is None else int(v_dim)
+        self.value_norm_eps = None if value_norm_eps is None else float(value_norm_eps)
+        if self.v_dim < 1 or self.v_dim > 512:
+            raise ValueError(f"value heads of width {self.v_dim}: the attention kernels take 1..512")
         self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(head_dim)
         self.position = POSITION_ENCODINGS.build(position) if position is not None else None
         qw, kw = n_heads * head_dim, n_kv_heads * head_dim
-        self.qkv = Linear([q_name, k_name, v_name], [qw, kw, kw], hidden)
-        self.out = Linear([o_name], [hidden], qw)
+        self.qkv = Linear([q_name, k_name, v_name], [qw, kw, n_kv_heads * self.v_dim], hidden)
+        self.out = Linear([o_name], [hidden], n_heads * self.v_dim)
         self.q_only: Linear | None = None
 
     def tensor_specs(self):
@@ -67,11 +77,27 @@ class Attention(Mixer):
         if rotation is None and n_kv == 0:
             return
         table, rot, interleaved = rotation if rotation is not None else (None, 0, False)
+        if self.own_store:
+            ctx.kernels.seq.kv_store(qkv, ctx.tok_pos, ctx.tok_seq, block_table, table, kpages, vpages, self.n_heads, n_kv,
+                                     self.head_dim, self.v_dim, rot, interleaved, self.value_norm_eps)
+            return
         ctx.kernels.rope_kv_write(qkv, ctx.tok_pos, ctx.tok_seq, block_table, table, kpages, vpages, self.n_heads, n_kv,
                                   self.head_dim, rot, interleaved)
 
     def cache_need(self):
-        return CacheNeed("window" if self.window else "full", self.n_kv_heads, self.head_dim, self.window)
+        return CacheNeed("window" if self.window else "full", self.n_kv_heads, self.head_dim, self.window,
+                         v_dim=None if self.v_dim == self.head_dim else self.v_dim)
+
+    @property
+    def own_store(self) -> bool:
+        """Keys and values go through `kv_store` (value norm, or values of another width than keys)."""
+        return self.value_norm_eps is not None or self.other_widths
+
+    @property
+    def other_widths(self) -> bool:
+        """Values of another width than keys, or a head width off the steps of 16 that the tiled and
+        tensor-core attention kernels are built for: `attn_wide_value` takes any."""
+        return self.v_dim != self.head_dim or self.head_dim % 16 != 0
 
     def takes_folded(self, ctx, rows: int) -> bool:
         """The q|k|v product can scale its own output rows: in a decode step of few rows, and in a long
@@ -94,9 +120,11 @@ class Attention(Mixer):
         rotation = self.position.rotation() if self.position is not None else None
         tc = ctx.kernels.tensor_core if x.dtype == torch.bfloat16 else None
         # a rotation can ride in the decode attention kernel, or in the q|k|v product of a long prompt step
-        fusion = rotation if (fast_decode and rotation is not None and DecodeKernels.rotation_fusable(*rotation[1:])) else None
+        fast_decode = fast_decode and not self.other_widths
+        fusion = rotation if (fast_decode and rotation is not None and not self.own_store
+                              and DecodeKernels.rotation_fusable(*rotation[1:])) else None
         fused_product = None
-        if (tc is not None and writes and not fast_decode and rotation is not None and x.shape[0] > tc.SKINNY_MAX_M
+        if (tc is not None and writes and not fast_decode and not self.own_store and rotation is not None and x.shape[0] > tc.SKINNY_MAX_M
                 and tc.rotation_fusable(self.head_dim, *rotation[1:]) and self.qkv.weight.dtype == torch.bfloat16
                 and tc.takes(x, self.qkv.weight)):
             fused_product = rotation
@@ -112,8 +140,11 @@ class Attention(Mixer):
             if fusion is None:
                 self._store(qkv, ctx, rotation, self.n_kv_heads if writes else 0, kpages if writes else None,
                             vpages if writes else None, block_table)
-        attn = torch.empty((x.shape[0], self.n_heads * self.head_dim), dtype=x.dtype, device=x.device)
-        if fast_decode:
+        attn = torch.empty((x.shape[0], self.n_heads * self.v_dim), dtype=x.dtype, device=x.device)
+        if self.other_widths:
+            ctx.kernels.seq.attn_wide_value(qkv, attn, ctx.tok_pos, ctx.tok_seq, block_table, kpages, vpages, self.n_heads,
+                                            self.n_kv_heads, self.head_dim, self.v_dim, self.window, self.scale)
+        elif fast_decode:
             n_split = ctx.decode_splits(self.n_heads, self.n_kv_heads, self.head_dim)
             scratch = torch.empty((ctx.n_seqs * self.n_heads * n_split * (self.head_dim + 2),), dtype=torch.float32,
                                   device=x.device)

@@ -35,9 +35,10 @@ from .base import ARRANGEMENTS, FEED_FORWARDS, MIXERS, NORMS, FoldRequest, PartS
 
 @dataclass(frozen=True)
 class LayerSpec:
-    """One layer as data: the arrangement and its parts by role."""
+    """One layer as data: the arrangement, its parts by role, and the arrangement's own constants."""
     arrangement: str
     parts: Mapping[str, PartSpec] = field(default_factory=dict)
+    params: Mapping[str, object] = field(default_factory=dict)
 
 
 def pre_norm_layer(mixer: PartSpec, feed_forward: PartSpec, mixer_norm: PartSpec, feed_forward_norm: PartSpec) -> LayerSpec:
@@ -132,7 +133,75 @@ class PreNormBlock(Block):
         return self.feed_forward.forward(n2, ctx, fold=fold) if fold is not None else self.feed_forward.forward(n2, ctx)
 
 
+class ScaledPreNormBlock(Block):
+    """x += m * mixer(c(norm(x))); then, if the layer has a feed-forward, x += m * feed_forward(norm(x)).
+
+    m (`residual_scale`) multiplies every sublayer's output on its way into the residual stream.
+    c (`input_conv`, optional) is a short causal convolution over time on each channel of what the
+    mixer reads, with the input added back: c(h) = h + conv(h); its last taps - 1 inputs are state
+    of the sequence like a recurrent mixer's. Roles: `mixer_norm`, `mixer`, and either both or
+    neither of `feed_forward_norm`, `feed_forward`. A sublayer's output goes on as weighted addends
+    (tensor, coefficient), so the norms named here must take those (`weighted_norm`); a mixer may
+    return such a list itself (branches side by side), and m multiplies its coefficients. The
+    unit's state is {"input_conv": ..., "mixer": ...} with whichever of the two exist."""
+
+    def __init__(self, spec: LayerSpec):
+        from .conv import CausalConv
+        self.mixer_norm = NORMS.build(_role(spec, "mixer_norm"))
+        self.mixer = MIXERS.build(_role(spec, "mixer"))
+        has = [r in spec.parts for r in ("feed_forward_norm", "feed_forward")]
+        if has[0] != has[1]:
+            raise ValueError("a layer has a feed-forward and its norm, or neither")
+        self.feed_forward_norm = NORMS.build(spec.parts["feed_forward_norm"]) if has[0] else None
+        self.feed_forward = FEED_FORWARDS.build(spec.parts["feed_forward"]) if has[1] else None
+        self.scale = float(spec.params.get("residual_scale", 1.0))
+        conv = spec.params.get("input_conv")
+        self.input_conv = CausalConv([conv["name"]], [int(conv["channels"])], int(conv["taps"]), residual=True) if conv else None
+
+    def parts(self):
+        out = [self.mixer_norm, self.mixer]
+        if self.input_conv is not None:
+            out.append(self.input_conv)
+        if self.feed_forward is not None:
+            out += [self.feed_forward_norm, self.feed_forward]
+        return out
+
+    def graph_safe(self) -> bool:
+        return all(getattr(p, "graph_safe", False) for p in self.parts() if p is not self.input_conv)
+
+    def state_need(self):
+        need = {}
+        if self.input_conv is not None and self.input_conv.state_need() is not None:
+            need["input_conv"] = self.input_conv.state_need()
+        if self.mixer.state_need() is not None:
+            need["mixer"] = self.mixer.state_need()
+        return need or None
+
+    def _scaled(self, y):
+        """A sublayer's output as addends with the residual scale applied."""
+        import torch
+        if isinstance(y, torch.Tensor):
+            return [(y[i], self.scale) for i in range(y.shape[0])] if y.dim() == 3 else [(y, self.scale)]
+        return [(t, c * self.scale) for t, c in y]
+
+    def forward(self, residual, delta, ctx, unit, writes):
+        st = ctx.unit_state(unit) if self.state_need() is not None else {}
+        h = self.mixer_norm.forward(residual, delta, ctx)
+        if self.input_conv is not None:
+            h = self.input_conv.forward(h, st.get("input_conv"), ctx, ctx.dtype)
+        if "mixer" in st:
+            a = self.mixer.forward(h, ctx, unit, writes, state=st["mixer"])
+        else:
+            a = self.mixer.forward(h, ctx, unit, writes)
+        a = self._scaled(a)
+        if self.feed_forward is None:
+            return a
+        n2 = self.feed_forward_norm.forward(residual, a, ctx)
+        return self._scaled(self.feed_forward.forward(n2, ctx))
+
+
 ARRANGEMENTS.register("pre_norm", PreNormBlock)
+ARRANGEMENTS.register("scaled_pre_norm", ScaledPreNormBlock)
 
 
 def build_block(spec: LayerSpec):

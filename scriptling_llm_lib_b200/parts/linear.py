@@ -80,33 +80,42 @@ class Linear:
             tc.gemm(a, w, out, ctx.err_flag, swiglu=swiglu_out is not None, owed=owed)
         return out
 
-    def forward(self, x: torch.Tensor, ctx, out_dtype=None, partials_ok: bool = False) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, ctx, out_dtype=None, partials_ok: bool = False, out=None) -> torch.Tensor:
         """y [T, out] in `out_dtype` (default: x's). With `partials_ok` the result may instead be
         float32 [P, T, out] partial sums that add up to y (the reader, a norm, adds them): a product
-        with few rows and few columns is split over K to fill the GPU."""
+        with few rows and few columns is split over K to fill the GPU. `x` may be a column slice of a
+        wider buffer (unit column stride). `out`: a contiguous [T, out] buffer of `out_dtype` to fill
+        instead of a new one (not with `partials_ok`)."""
         w = self.weight
         out_dtype = out_dtype or x.dtype
+        if out is not None:
+            if partials_ok or out.dtype != out_dtype or tuple(out.shape) != (x.shape[0], w.shape[0]) or not out.is_contiguous():
+                raise ValueError(f"out must be a contiguous {out_dtype} [{x.shape[0]}, {w.shape[0]}] buffer")
+            given = out
+            torch_empty = lambda shape, dtype, device: given          # noqa: E731
+        else:
+            torch_empty = lambda shape, dtype, device: torch.empty(shape, dtype=dtype, device=device)   # noqa: E731
         if w.dtype == x.dtype:
             if x.dtype == torch.bfloat16 and ctx.kernels.tensor_core.prefers_skinny(x, w, "partials" if partials_ok else "plain", ctx.engine.sm_count):
                 tc = ctx.kernels.tensor_core
                 split = tc.skinny_split(w.shape[0], w.shape[1], ctx.engine.sm_count) if partials_ok else 1
                 shape = (split, x.shape[0], w.shape[0]) if split > 1 else (x.shape[0], w.shape[0])
-                out = torch.empty(shape, dtype=torch.float32 if split > 1 else out_dtype, device=x.device)
+                out = torch_empty(shape, torch.float32 if split > 1 else out_dtype, x.device)
                 tc.gemm_skinny(x, w, out, ctx.err_flag)
                 return out
             if x.dtype == torch.bfloat16 and ctx.kernels.decode.prefers(x, w, ctx.engine.sm_count):
                 split = ctx.kernels.decode.split_for(w.shape[0], w.shape[1], ctx.engine.sm_count) if partials_ok else 1
                 shape = (split, x.shape[0], w.shape[0]) if split > 1 else (x.shape[0], w.shape[0])
-                out = torch.empty(shape, dtype=torch.float32 if split > 1 else out_dtype, device=x.device)
+                out = torch_empty(shape, torch.float32 if split > 1 else out_dtype, x.device)
                 ctx.kernels.decode.gemm_small_m(x, w, out)
                 return out
             if x.dtype == torch.bfloat16 and ctx.kernels.tensor_core.takes(x, w):
-                out = torch.empty((x.shape[0], w.shape[0]), dtype=out_dtype, device=x.device)
+                out = torch_empty((x.shape[0], w.shape[0]), out_dtype, x.device)
                 ctx.kernels.tensor_core.gemm(x, w, out, ctx.err_flag)
                 return out
             split = ctx.kernels.gemm_nt_split(x.shape[0], w.shape[0], w.shape[1], ctx.engine.sm_count) if partials_ok else 1
             shape = (split, x.shape[0], w.shape[0]) if split > 1 else (x.shape[0], w.shape[0])
-            out = torch.empty(shape, dtype=torch.float32 if split > 1 else out_dtype, device=x.device)
+            out = torch_empty(shape, torch.float32 if split > 1 else out_dtype, x.device)
             ctx.kernels.gemm_nt(x, w, out)
             return out
         if w.dtype == torch.float32 and x.dtype == torch.bfloat16:

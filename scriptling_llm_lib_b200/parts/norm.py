@@ -39,4 +39,40 @@ class RMSNorm(Norm):
         return y
 
 
+class WeightedNorm(Norm):
+    """A norm with a weight and no bias in front of which the residual stream takes several
+    addends, each with a coefficient: v = residual + sum c_i * a_i, then, with `center`,
+    y = (v - mean(v)) / sqrt(mean((v - mean(v))^2) + eps) * w (layer norm), else
+    y = v / sqrt(mean(v^2) + eps) * w. Sum, mean, variance and division are float32 whatever the
+    engine's dtype. `delta`: None, one tensor [T, width] (coefficient 1), or a list of
+    (tensor, coefficient); the tensors are float32 or of the engine's dtype. `out_dtype="float32"`
+    keeps the normed rows in float32 for a reader that works on them before rounding (a short
+    convolution in front of the mixer)."""
+    graph_safe = True
+
+    def __init__(self, width: int, eps: float, weight_name: str, center: bool = True, out_dtype: str | None = None):
+        self.width, self.eps, self.weight_name, self.center = width, float(eps), weight_name, bool(center)
+        self.out_dtype = {None: None, "float32": torch.float32}[out_dtype]
+        self.weight = None
+
+    def tensor_specs(self):
+        return [TensorSpec(self.weight_name, (self.width,), init="norm_weight")]
+
+    def bind(self, tensors, dtype, device):
+        self.weight = tensors[self.weight_name]
+
+    def forward(self, residual, delta, ctx, rows=None):
+        addends = []
+        for t, c in ([] if delta is None else [(delta, 1.0)] if isinstance(delta, torch.Tensor) else delta):
+            if t.dim() == 3:                # partial sums of a product whose K range was split: each is an addend
+                addends += [(t[i], c) for i in range(t.shape[0])]
+            else:
+                addends.append((t, c))
+        n = residual.shape[0] if rows is None else rows.shape[0]
+        y = torch.empty((n, self.width), dtype=self.out_dtype or ctx.dtype, device=residual.device)
+        ctx.kernels.seq.add_norm(residual, addends, rows, self.weight, y, self.eps, self.center)
+        return y
+
+
 NORMS.register("rmsnorm", RMSNorm)
+NORMS.register("weighted_norm", WeightedNorm)

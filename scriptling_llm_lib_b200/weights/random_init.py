@@ -51,6 +51,10 @@ INIT_LAWS: dict[str, Normal | UniformInteger] = {
     "matrix": Normal(0.0, MATRIX_STD),
     "norm_weight": Normal(1.0, MATRIX_STD),
     "integer_table": UniformInteger(2 ** 15),
+    "conv_filter": Normal(0.0, 0.3),        # the taps of a short convolution over time
+    "bias": Normal(0.0, 0.1),
+    "log_rate": Normal(0.0, 0.5),           # logarithms of decay rates (a recurrence's A_log, lambda)
+    "gate_matrix": Normal(0.0, 0.05),       # the small square blocks of block-diagonal gates
 }
 
 
