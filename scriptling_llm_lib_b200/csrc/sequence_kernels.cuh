@@ -288,53 +288,77 @@ __global__ void delta_prepare_kernel(float* __restrict__ qk, int ld_qk, const fl
   }
 }
 
-// The recurrence itself. One warp per (32 value columns, head, sequence); a lane owns one column j of the
-// head's state S [dk][dv] (row-major in the state tensor [slot][H][dk][dv]) in registers and walks the
-// sequence's rows in order: S *= decay; u = beta * (v_j - sum_d S[d] k[d]); S[d] += k[d] u; o_j = sum_d S[d] q[d].
-// q and k of a row are staged in shared memory by the warp. DK >= dk is the register array's length.
-template <int DK>
+// The recurrence itself. One warp per (8 value columns, head, sequence): four lanes share a column j of the
+// head's state S [dk][dv] (row-major in the state tensor [slot][H][dk][dv]), lane r of them keeping rows
+// r, r + 4, r + 8, ... in registers, and the warp walks the sequence's rows in order:
+//   S *= decay;  u = beta * (v_j - sum_d S[d] k[d]);  S[d] += k[d] u;  o_j = sum_d S[d] q[d]
+// (the two sums end with two shuffles among the four lanes). q and k of a row are staged in shared memory
+// by the warp, the next row's being fetched while this row is worked on. DKR rows per lane: dk <= 4 DKR.
+template <int DKR>
 __global__ void __launch_bounds__(32) delta_rule_kernel(const float* __restrict__ qk, int ld_qk, const float* __restrict__ v,
                                                          int ld_v, const float* __restrict__ bd, float* __restrict__ state,
                                                          const int* __restrict__ seq_start, const int* __restrict__ slots,
                                                          float* __restrict__ o, int H, int G, int dk, int dv) {
-  __shared__ float sq[DK], sk[DK];
-  int lane = threadIdx.x;
-  int j = blockIdx.x * 32 + lane, h = blockIdx.y, b = blockIdx.z;
+  constexpr int DKP = 4 * DKR;                  // key width with padding (zeros)
+  constexpr int NL = (DKP + 31) / 32;           // staged values per lane
+  __shared__ float sq[2][DKP], sk[2][DKP];
+  int lane = threadIdx.x, r = lane & 3;
+  int j = blockIdx.x * 8 + (lane >> 2), h = blockIdx.y, b = blockIdx.z;
   int g = h / (H / G);
   bool live = j < dv;
   float* Sg = state + (((size_t)slots[b] * H + h) * dk) * dv + j;
-  float S[DK];
+  float S[DKR];
 #pragma unroll
-  for (int d = 0; d < DK; d++) S[d] = (live && d < dk) ? Sg[(size_t)d * dv] : 0.f;
-  for (int d = dk + lane; d < DK; d += 32) { sq[d] = 0.f; sk[d] = 0.f; }
+  for (int i = 0; i < DKR; i++) S[i] = (live && r + 4 * i < dk) ? Sg[(size_t)(r + 4 * i) * dv] : 0.f;
   int t0 = seq_start[b], t1 = seq_start[b + 1];
-  for (int t = t0; t < t1; t++) {
-    __syncwarp();
+  float rq[NL], rk[NL], beta = 0.f, decay = 0.f, vj = 0.f;
+  auto fetch = [&](int t) {
     const float* qr = qk + (size_t)t * ld_qk + (size_t)g * dk;
     const float* kr = qr + (size_t)G * dk;
-    for (int d = lane; d < dk; d += 32) { sq[d] = qr[d]; sk[d] = kr[d]; }
-    float beta = bd[(size_t)t * 2 * H + h], decay = bd[(size_t)t * 2 * H + H + h];
-    float vj = live ? v[(size_t)t * ld_v + (size_t)h * dv + j] : 0.f;
+#pragma unroll
+    for (int i = 0; i < NL; i++) {
+      int d = lane + 32 * i;
+      rq[i] = d < dk ? qr[d] : 0.f;
+      rk[i] = d < dk ? kr[d] : 0.f;
+    }
+    beta = bd[(size_t)t * 2 * H + h];
+    decay = bd[(size_t)t * 2 * H + H + h];
+    vj = live ? v[(size_t)t * ld_v + (size_t)h * dv + j] : 0.f;
+  };
+  if (t0 < t1) fetch(t0);
+  for (int t = t0; t < t1; t++) {
+    int buf = (t - t0) & 1;
+#pragma unroll
+    for (int i = 0; i < NL; i++) {
+      int d = lane + 32 * i;
+      if (d < DKP) { sq[buf][d] = rq[i]; sk[buf][d] = rk[i]; }
+    }
+    float be = beta, de = decay, vv = vj;
     __syncwarp();
+    if (t + 1 < t1) fetch(t + 1);
     float dot = 0.f;
 #pragma unroll
-    for (int d = 0; d < DK; d++) {
-      S[d] *= decay;
-      dot += S[d] * sk[d];
+    for (int i = 0; i < DKR; i++) {
+      S[i] *= de;
+      dot += S[i] * sk[buf][r + 4 * i];
     }
-    float u = beta * (vj - dot);
+    dot += __shfl_xor_sync(0xffffffffu, dot, 1);
+    dot += __shfl_xor_sync(0xffffffffu, dot, 2);
+    float u = be * (vv - dot);
     float oj = 0.f;
 #pragma unroll
-    for (int d = 0; d < DK; d++) {
-      S[d] += sk[d] * u;
-      oj += S[d] * sq[d];
+    for (int i = 0; i < DKR; i++) {
+      S[i] += sk[buf][r + 4 * i] * u;
+      oj += S[i] * sq[buf][r + 4 * i];
     }
-    if (live) o[(size_t)t * H * dv + (size_t)h * dv + j] = oj;
+    oj += __shfl_xor_sync(0xffffffffu, oj, 1);
+    oj += __shfl_xor_sync(0xffffffffu, oj, 2);
+    if (live && r == 0) o[(size_t)t * H * dv + (size_t)h * dv + j] = oj;
   }
   if (live) {
 #pragma unroll
-    for (int d = 0; d < DK; d++)
-      if (d < dk) Sg[(size_t)d * dv] = S[d];
+    for (int i = 0; i < DKR; i++)
+      if (r + 4 * i < dk) Sg[(size_t)(r + 4 * i) * dv] = S[i];
   }
 }
 

@@ -68,9 +68,9 @@ def test_replay_cuttings(tmp_path, name, dtype):
 def test_replay_refuses_more_than_the_cache_holds(tmp_path):
     raw, seed = TINY["A"]
     d = make_model_dir(tmp_path / "model", raw, seed)
-    rp = Replay(d, "float32", tmp_path / "out", 64, 256)
+    rp = Replay(d, "float32", tmp_path / "out", 64, 256)      # one page for the tokens and one to spare
     with pytest.raises(AssertionError):
-        rp.step([("a", random_ids(65, 256, 0), [0])])
+        rp.step([("a", random_ids(129, 256, 0), [0])])
     assert rp.close() != 0
 
 
