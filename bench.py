@@ -441,6 +441,75 @@ def run(args):
     return 0
 
 
+# ------------------------------------------------------------------ another design beside its closest model
+# Layer sizes that resemble a real model's, for the Sozilix decoder (windowed attention beside a gated delta
+# rule, then two gated linear recurrences, repeated) and for the Llama decoder of the same width, depth, heads,
+# feed-forward and window. `left` widths: keys/values of 128 go through the library's attention kernels, the
+# third size (keys 64, values 128) through the kernel that takes values of another width.
+DESIGN_SIZES = {
+    "w1024": dict(width=1024, heads=8, kv_heads=2, dim=128, vdim=128, window=512, ff=4096, lru=1280, blocks=5, groups=2),
+    "w2048": dict(width=2048, heads=16, kv_heads=4, dim=128, vdim=128, window=1024, ff=8192, lru=2560, blocks=10, groups=2),
+    "w2048-k64": dict(width=2048, heads=16, kv_heads=4, dim=64, vdim=128, window=1024, ff=8192, lru=2560, blocks=10, groups=2),
+}
+DESIGN_VOCAB = 32000
+
+
+def sozilix_config(z):
+    par = {"type": "parallel", "mlp": {"ff": z["ff"], "kind": "dense"}, "mixer": {
+        "left": {"dim": z["dim"], "heads": z["heads"], "kv_heads": z["kv_heads"], "mask": {"size": z["window"]},
+                 "rot": {"base": 10000.0, "dims": z["dim"] // 2}, "scale": z["dim"] ** -0.5, "vdim": z["vdim"]},
+        "left_scale": 1.0, "right_scale": 1.0,
+        "right": {"conv": 4, "dim": 128, "heads": z["heads"], "kv_heads": z["heads"] // 2, "vdim": 128}}}
+    lru = {"type": "rglru", "mlp": None, "mixer": {"width": z["lru"], "blocks": z["blocks"], "conv": 4}}
+    return {"architecture": "Sozilix", "canon": {"taps": 4}, "layers": [par, lru, lru] * z["groups"], "norm": {"eps": 1e-5},
+            "residual_mult": 1.0, "vocab": DESIGN_VOCAB, "width": z["width"]}
+
+
+def llama_like(z, max_positions):
+    return {"architectures": ["LlamaForCausalLM"], "model_type": "llama", "num_hidden_layers": 3 * z["groups"],
+            "hidden_size": z["width"], "num_attention_heads": z["heads"], "num_key_value_heads": z["kv_heads"],
+            "head_dim": max(z["dim"], z["vdim"]), "intermediate_size": z["ff"], "vocab_size": DESIGN_VOCAB, "rope_theta": 10000.0,
+            "rms_norm_eps": 1e-5, "tie_word_embeddings": False, "max_position_embeddings": max_positions,
+            "sliding_window": z["window"], "hidden_act": "silu"}
+
+
+def design_compare(args):
+    """Prompt-step and decode throughput of the Sozilix decoder at DESIGN_SIZES beside the Llama decoder of
+    equal size (random weights, bfloat16 unless --dtype says otherwise); one JSON line."""
+    pk = peaks()
+    tmp = tempfile.mkdtemp(prefix="sllm_bench_")
+    b = Bench(args, pk, tmp)
+    out = {"metric": "design_compare", "design": args.design, "dtype": args.dtype, "data": "synthetic, random weights",
+           "prefill_tokens": args.prefill_tokens, "decode": {"batch": args.batch, "context": args.context, "steps": args.steps,
+                                                             "warmup": args.warmup}, "sizes": {}}
+    for name in (args.design_sizes.split(",") if args.design_sizes else DESIGN_SIZES):
+        z = DESIGN_SIZES[name]
+        rec = {}
+        for which, raw in (("sozilix", sozilix_config(z)), ("llama", llama_like(z, args.context + args.prefill_tokens + 64))):
+            path = os.path.join(tmp, f"{name}-{which}.json")
+            with open(path, "w") as f:
+                json.dump(raw, f)
+            eng, sampler = b.load(f"random:{path}:0", args.dtype, max(args.batch * (args.context + 64), args.prefill_tokens + 64),
+                                  args.batch)
+            n_params = sum(p.elements_read_per_step() for e in eng.layout.schedule for p in eng.model.blocks[e.layer].parts())
+            r = {"layer_params": n_params}
+            if args.only != "decode":
+                ms = b.time_prompt_step(eng, [args.prefill_tokens], 1)
+                r["prefill"] = {"ms": round(ms, 3), "tok_s": round(args.prefill_tokens / ms * 1e3, 1),
+                                "matrix_tflops": round(2 * n_params * args.prefill_tokens / (ms * 1e-3) / 1e12, 1)}
+            if args.only != "prefill":
+                lens = b.equal_prompts(args.batch, args.steps, args.warmup)
+                ms, _, launches = b.time_decode(eng, sampler, lens, args.steps, args.warmup, 3)
+                r["decode"] = {"ms": round(ms, 4), "tok_s": round(args.batch / ms * 1e3, 1), "launches_per_step": launches,
+                               "weights_gbs": round(WIDTH[args.dtype] * (n_params + DESIGN_VOCAB * z["width"]) / (ms * 1e-3) / 1e9, 1)}
+            rec[which] = r
+        out["sizes"][name] = rec
+    import shutil
+    shutil.rmtree(tmp, ignore_errors=True)
+    print(json.dumps(out))
+    return 0
+
+
 def kernel_alone(args):
     """One decode kernel by itself, as profiles/ quotes it: launched back to back in a CUDA graph over
     inputs that rotate through more bytes than L2 holds, timed with CUDA events; one JSON line per case.
@@ -548,6 +617,11 @@ def main():
                     help="run one part only (a small case to profile); the JSON line then holds that part alone")
     ap.add_argument("--kernel", default=None, choices=["attn_decode", "gemm_small_m"],
                     help="time one decode kernel alone at --shape, --batch (and --context) instead of the model")
+    ap.add_argument("--design", default=None, choices=["sozilix"],
+                    help="measure this design's prompt step and decoding at a few real layer sizes beside the Llama decoder "
+                         "of equal size (--prefill-tokens, --batch, --context, --steps, --dtype, --only apply) instead of the "
+                         "headline run")
+    ap.add_argument("--design-sizes", dest="design_sizes", default=None, help="comma-separated names out of DESIGN_SIZES")
     args = ap.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable": "the reference is a Go package (go.mod) with CPU-only code; "
@@ -559,6 +633,8 @@ def main():
     args.warmup = max(3, args.warmup)
     if args.kernel is not None:
         return kernel_alone(args)
+    if args.design is not None:
+        return design_compare(args)
     return run(args)
 
 

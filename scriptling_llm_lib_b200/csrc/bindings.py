@@ -672,17 +672,24 @@ class SequenceKernels:
                                           _ptr(y, self.dtype, "y"), c_int(o.shape[0]), c_int(n_heads), c_int(dv), c_float(eps),
                                           _stream()), "gated_unit_rms")
 
+    SCAN_WALK_MAX = 4     # rows of a sequence in one step up to which a thread walks them one after the other
+
     def rglru_scan(self, gates, u, yraw, ra_b, ri_b, lam, y_b, state, ctx, out, block_size):
         """gates float32 [blocks, T, 2 * block_size], u float32 [T, W], yraw [T, W] view of the element type,
         state float32 [slots, W] (read and advanced), out [T, W] of the element type."""
         T, W = u.shape
         if gates.dtype != torch.float32 or tuple(gates.shape) != (W // block_size, T, 2 * block_size) or yraw.dtype != self.dtype:
             raise KernelError(f"rglru_scan shapes: gates {tuple(gates.shape)} {gates.dtype}, u {tuple(u.shape)}")
+        scratch = None
+        if ctx.max_new > self.SCAN_WALK_MAX:        # a long portion: the scan runs in pieces, which need room for their ends
+            piece = self._fn("rglru_piece_rows")()
+            scratch = torch.empty((2 * ctx.n_seqs * -(-ctx.max_new // piece) * W,), dtype=torch.float32, device=u.device)
         _check(self._fn("rglru_scan")(_ptr(gates, torch.float32, "gates"), _ptr(u, torch.float32, "u"), self._view(yraw, "yraw"),
                                       c_int(yraw.stride(0)), _ptr(ra_b, None, "ra_b"), _ptr(ri_b, None, "ri_b"),
                                       _ptr(lam, None, "lam"), _ptr(y_b, None, "y_b"), c_int(self._flag(lam, "lam")),
                                       _ptr(state, torch.float32, "state"), _ptr(ctx.seq_start, torch.int32, "seq_start"),
-                                      _ptr(ctx.slots, torch.int32, "slots"), _ptr(out, self.dtype, "out"), c_int(T),
+                                      _ptr(ctx.slots, torch.int32, "slots"), _ptr(out, self.dtype, "out"),
+                                      _ptr(scratch, torch.float32, "scratch"), c_int(max(1, ctx.max_new)), c_int(T),
                                       c_int(ctx.n_seqs), c_int(W), c_int(block_size), _stream()), "rglru_scan")
 
 

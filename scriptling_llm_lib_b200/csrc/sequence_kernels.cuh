@@ -289,19 +289,22 @@ __global__ void delta_prepare_kernel(float* __restrict__ qk, int ld_qk, const fl
 }
 
 // The recurrence itself. One warp per (8 value columns, head, sequence): four lanes share a column j of the
-// head's state S [dk][dv] (row-major in the state tensor [slot][H][dk][dv]), lane r of them keeping rows
-// r, r + 4, r + 8, ... in registers, and the warp walks the sequence's rows in order:
+// head's state S [dk][dv] (row-major in the state tensor [slot][H][dk][dv]); lane r of them keeps the rows
+// 16 m + 4 r + (0..3), m = 0, 1, ..., in registers, and the warp walks the sequence's rows in order:
 //   S *= decay;  u = beta * (v_j - sum_d S[d] k[d]);  S[d] += k[d] u;  o_j = sum_d S[d] q[d]
-// (the two sums end with two shuffles among the four lanes). q and k of a row are staged in shared memory
-// by the warp, the next row's being fetched while this row is worked on. DKR rows per lane: dk <= 4 DKR.
+// (each sum runs in four partial sums and ends with two shuffles among the four lanes). q and k of a row are
+// staged in shared memory by the warp and read back 16 bytes at a time, the next row's being fetched while
+// this row is worked on. DKR rows per lane (a multiple of 4): dk <= 4 DKR.
 template <int DKR>
 __global__ void __launch_bounds__(32) delta_rule_kernel(const float* __restrict__ qk, int ld_qk, const float* __restrict__ v,
                                                          int ld_v, const float* __restrict__ bd, float* __restrict__ state,
                                                          const int* __restrict__ seq_start, const int* __restrict__ slots,
                                                          float* __restrict__ o, int H, int G, int dk, int dv) {
+  static_assert(DKR % 4 == 0, "a lane keeps whole quads of rows");
   constexpr int DKP = 4 * DKR;                  // key width with padding (zeros)
   constexpr int NL = (DKP + 31) / 32;           // staged values per lane
-  __shared__ float sq[2][DKP], sk[2][DKP];
+  constexpr int NQ = DKR / 4;                   // quads per lane
+  __shared__ __align__(16) float sq[2][DKP], sk[2][DKP];
   int lane = threadIdx.x, r = lane & 3;
   int j = blockIdx.x * 8 + (lane >> 2), h = blockIdx.y, b = blockIdx.z;
   int g = h / (H / G);
@@ -309,7 +312,10 @@ __global__ void __launch_bounds__(32) delta_rule_kernel(const float* __restrict_
   float* Sg = state + (((size_t)slots[b] * H + h) * dk) * dv + j;
   float S[DKR];
 #pragma unroll
-  for (int i = 0; i < DKR; i++) S[i] = (live && r + 4 * i < dk) ? Sg[(size_t)(r + 4 * i) * dv] : 0.f;
+  for (int i = 0; i < DKR; i++) {
+    int d = 16 * (i >> 2) + 4 * r + (i & 3);
+    S[i] = (live && d < dk) ? Sg[(size_t)d * dv] : 0.f;
+  }
   int t0 = seq_start[b], t1 = seq_start[b + 1];
   float rq[NL], rk[NL], beta = 0.f, decay = 0.f, vj = 0.f;
   auto fetch = [&](int t) {
@@ -336,29 +342,36 @@ __global__ void __launch_bounds__(32) delta_rule_kernel(const float* __restrict_
     float be = beta, de = decay, vv = vj;
     __syncwarp();
     if (t + 1 < t1) fetch(t + 1);
-    float dot = 0.f;
+    float4 kq[NQ];
+    float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
 #pragma unroll
-    for (int i = 0; i < DKR; i++) {
-      S[i] *= de;
-      dot += S[i] * sk[buf][r + 4 * i];
+    for (int m = 0; m < NQ; m++) {
+      kq[m] = *(const float4*)&sk[buf][16 * m + 4 * r];
+      S[4 * m] *= de; S[4 * m + 1] *= de; S[4 * m + 2] *= de; S[4 * m + 3] *= de;
+      d0 += S[4 * m] * kq[m].x; d1 += S[4 * m + 1] * kq[m].y; d2 += S[4 * m + 2] * kq[m].z; d3 += S[4 * m + 3] * kq[m].w;
     }
+    float dot = (d0 + d1) + (d2 + d3);
     dot += __shfl_xor_sync(0xffffffffu, dot, 1);
     dot += __shfl_xor_sync(0xffffffffu, dot, 2);
     float u = be * (vv - dot);
-    float oj = 0.f;
+    d0 = d1 = d2 = d3 = 0.f;
 #pragma unroll
-    for (int i = 0; i < DKR; i++) {
-      S[i] += sk[buf][r + 4 * i] * u;
-      oj += S[i] * sq[buf][r + 4 * i];
+    for (int m = 0; m < NQ; m++) {
+      float4 qq = *(const float4*)&sq[buf][16 * m + 4 * r];
+      S[4 * m] += kq[m].x * u; S[4 * m + 1] += kq[m].y * u; S[4 * m + 2] += kq[m].z * u; S[4 * m + 3] += kq[m].w * u;
+      d0 += S[4 * m] * qq.x; d1 += S[4 * m + 1] * qq.y; d2 += S[4 * m + 2] * qq.z; d3 += S[4 * m + 3] * qq.w;
     }
+    float oj = (d0 + d1) + (d2 + d3);
     oj += __shfl_xor_sync(0xffffffffu, oj, 1);
     oj += __shfl_xor_sync(0xffffffffu, oj, 2);
     if (live && r == 0) o[(size_t)t * H * dv + (size_t)h * dv + j] = oj;
   }
   if (live) {
 #pragma unroll
-    for (int i = 0; i < DKR; i++)
-      if (r + 4 * i < dk) Sg[(size_t)(r + 4 * i) * dv] = S[i];
+    for (int i = 0; i < DKR; i++) {
+      int d = 16 * (i >> 2) + 4 * r + (i & 3);
+      if (d < dk) Sg[(size_t)d * dv] = S[i];
+    }
   }
 }
 
@@ -385,30 +398,110 @@ __global__ void gated_unit_rms_kernel(const float* __restrict__ o, const A* __re
 // Channel c of width W lies in block c / bs of the gates; gates[block][t][0..bs) is the raw recurrence gate,
 // [bs..2bs) the raw input gate (block-diagonal products of u, float). r = sigmoid(. + ra_b), i = sigmoid(. + ri_b),
 // a = exp(-8 r softplus(lam)); S = a S + sqrt(1 - a^2) i u from the sequence's state [slot][W];
-// out[t][c] = S * gelu_tanh(yraw[t][c] + y_b[c]). A thread per (sequence, channel).
+// out[t][c] = S * gelu_tanh(yraw[t][c] + y_b[c]).
+struct LruArgs {
+  const float* gates; const float* u; const void* yraw; int ld_y;
+  const void* ra_b; const void* ri_b; const void* lam; const void* y_b; int w_f32;
+  float* state; const int* seq_start; const int* slots; void* out;
+  int T, W, bs;
+};
+
+struct LruChannel {       // what a thread knows of its channel
+  float sp, rb, ib, yb;
+  const float* gb;
+  int c, cc, bs;
+};
+
+__device__ __forceinline__ LruChannel lru_channel(const LruArgs& p, int c) {
+  LruChannel ch;
+  ch.c = c; ch.bs = p.bs; ch.cc = c % p.bs;
+  ch.sp = softplus_f(load_w(p.lam, p.w_f32, c));
+  ch.rb = load_w(p.ra_b, p.w_f32, c); ch.ib = load_w(p.ri_b, p.w_f32, c); ch.yb = load_w(p.y_b, p.w_f32, c);
+  ch.gb = p.gates + (size_t)(c / p.bs) * p.T * 2 * p.bs;
+  return ch;
+}
+
+// a_t and b_t of S_t = a_t S_{t-1} + b_t for row t
+__device__ __forceinline__ void lru_terms(const LruArgs& p, const LruChannel& ch, int t, float& a, float& bt) {
+  float r = sigmoid_f(ch.gb[(size_t)t * 2 * ch.bs + ch.cc] + ch.rb);
+  float i = sigmoid_f(ch.gb[(size_t)t * 2 * ch.bs + ch.bs + ch.cc] + ch.ib);
+  float log_a = -8.0f * r * ch.sp;
+  a = expf(log_a);
+  bt = sqrtf(-expm1f(2.0f * log_a)) * (i * p.u[(size_t)t * p.W + ch.c]);      // 1 - a^2 without cancellation
+}
+
+// A thread per (sequence, channel) walks the sequence's rows: the decode step, and short portions.
 template <typename A>
-__global__ void rglru_scan_kernel(const float* __restrict__ gates, const float* __restrict__ u, const A* __restrict__ yraw,
-                                  int ld_y, const void* __restrict__ ra_b, const void* __restrict__ ri_b,
-                                  const void* __restrict__ lam, const void* __restrict__ y_b, int w_f32,
-                                  float* __restrict__ state, const int* __restrict__ seq_start, const int* __restrict__ slots,
-                                  A* __restrict__ out, int T, int W, int bs) {
+__global__ void rglru_scan_kernel(LruArgs p) {
   int b = blockIdx.x;
   int c = blockIdx.y * blockDim.x + threadIdx.x;
-  if (c >= W) return;
-  int blk = c / bs, cc = c % bs;
-  float sp = softplus_f(load_w(lam, w_f32, c));
-  float rb = load_w(ra_b, w_f32, c), ib = load_w(ri_b, w_f32, c), yb = load_w(y_b, w_f32, c);
-  float* sp_state = state + (size_t)slots[b] * W + c;
+  if (c >= p.W) return;
+  LruChannel ch = lru_channel(p, c);
+  float* sp_state = p.state + (size_t)p.slots[b] * p.W + c;
   float S = *sp_state;
-  const float* gb = gates + (size_t)blk * T * 2 * bs;
-  int t0 = seq_start[b], t1 = seq_start[b + 1];
+  int t0 = p.seq_start[b], t1 = p.seq_start[b + 1];
   for (int t = t0; t < t1; t++) {
-    float r = sigmoid_f(gb[(size_t)t * 2 * bs + cc] + rb);
-    float i = sigmoid_f(gb[(size_t)t * 2 * bs + bs + cc] + ib);
-    float log_a = -8.0f * r * sp;
-    float a = expf(log_a);
-    S = a * S + sqrtf(-expm1f(2.0f * log_a)) * (i * u[(size_t)t * W + c]);      // 1 - a^2 without cancellation
-    out[(size_t)t * W + c] = from_f32<A>(S * gelu_tanh_f(to_f32(yraw[(size_t)t * ld_y + c]) + yb));
+    float a, bt;
+    lru_terms(p, ch, t, a, bt);
+    S = a * S + bt;
+    ((A*)p.out)[(size_t)t * p.W + c] = from_f32<A>(S * gelu_tanh_f(to_f32(((const A*)p.yraw)[(size_t)t * p.ld_y + c]) + ch.yb));
   }
   *sp_state = S;
+}
+
+// Long portions, in three kernels. The rows of a sequence are cut into pieces of LRU_PIECE. (1) A thread per
+// (piece, channel) runs its piece from S = 0 and leaves the piece's product of a and its end value:
+// S_end = prod * S_start + end. (2) A thread per (sequence, channel) carries the state from piece to piece
+// and leaves every piece's S_start (the sequence's state is advanced here). (3) A thread per (piece, channel)
+// runs its piece again from S_start and writes the rows. `pieces` = most pieces of any sequence.
+#define LRU_PIECE 32
+template <typename A>
+__global__ void rglru_piece_kernel(LruArgs p, float* __restrict__ prod, float* __restrict__ end, int pieces) {
+  int b = blockIdx.x / pieces, k = blockIdx.x % pieces;
+  int c = blockIdx.y * blockDim.x + threadIdx.x;
+  int t0 = p.seq_start[b] + k * LRU_PIECE, t1 = min(p.seq_start[b + 1], t0 + LRU_PIECE);
+  if (c >= p.W || t0 >= t1) return;
+  LruChannel ch = lru_channel(p, c);
+  float P = 1.f, S = 0.f;
+  for (int t = t0; t < t1; t++) {
+    float a, bt;
+    lru_terms(p, ch, t, a, bt);
+    S = a * S + bt;
+    P *= a;
+  }
+  prod[(size_t)blockIdx.x * p.W + c] = P;
+  end[(size_t)blockIdx.x * p.W + c] = S;
+}
+
+__global__ void rglru_carry_kernel(LruArgs p, const float* __restrict__ prod, float* __restrict__ end, int pieces) {
+  int b = blockIdx.x;
+  int c = blockIdx.y * blockDim.x + threadIdx.x;
+  if (c >= p.W) return;
+  float* sp_state = p.state + (size_t)p.slots[b] * p.W + c;
+  float S = *sp_state;
+  int n = p.seq_start[b + 1] - p.seq_start[b];
+  int used = (n + LRU_PIECE - 1) / LRU_PIECE;
+  for (int k = 0; k < used; k++) {
+    size_t at = ((size_t)b * pieces + k) * p.W + c;
+    float next = prod[at] * S + end[at];
+    end[at] = S;                                // from here on: the piece's start value
+    S = next;
+  }
+  *sp_state = S;
+}
+
+template <typename A>
+__global__ void rglru_write_kernel(LruArgs p, const float* __restrict__ start, int pieces) {
+  int b = blockIdx.x / pieces, k = blockIdx.x % pieces;
+  int c = blockIdx.y * blockDim.x + threadIdx.x;
+  int t0 = p.seq_start[b] + k * LRU_PIECE, t1 = min(p.seq_start[b + 1], t0 + LRU_PIECE);
+  if (c >= p.W || t0 >= t1) return;
+  LruChannel ch = lru_channel(p, c);
+  float S = start[(size_t)blockIdx.x * p.W + c];
+  for (int t = t0; t < t1; t++) {
+    float a, bt;
+    lru_terms(p, ch, t, a, bt);
+    S = a * S + bt;
+    ((A*)p.out)[(size_t)t * p.W + c] = from_f32<A>(S * gelu_tanh_f(to_f32(((const A*)p.yraw)[(size_t)t * p.ld_y + c]) + ch.yb));
+  }
 }
