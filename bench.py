@@ -510,6 +510,125 @@ def design_compare(args):
     return 0
 
 
+def sequence_kernels_alone(args):
+    """The kernels of the mixers with state, each alone at the sizes of DESIGN_SIZES[--design-sizes or w2048]: a prompt
+    of --prefill-tokens rows and a decode step of --batch rows; a JSON line each with the time (CUDA events around a
+    captured run of launches whose inputs rotate through more than L2 holds) and what it is of the HBM copy rate or
+    of the float FMA rate."""
+    import torch
+    from scriptling_llm_lib_b200.csrc.bindings import KernelSet, ProbeKernels
+    pk = peaks()
+    z = DESIGN_SIZES[(args.design_sizes or "w2048").split(",")[0]]
+    dt = {"bfloat16": torch.bfloat16, "float32": torch.float32}[args.dtype]
+    k = KernelSet(dt).seq
+    fma = ProbeKernels().fma_tflops()
+    dev = "cuda"
+    W, H, G, dk, dv, LW, bs = z["width"], z["heads"], z["heads"] // 2, 128, 128, z["lru"], z["lru"] // z["blocks"]
+    AH, AG, hd, vd, window = z["heads"], z["kv_heads"], z["dim"], z["vdim"], z["window"]
+    esz = 2 if dt == torch.bfloat16 else 4
+
+    class Ctx:
+        pass
+
+    def timed(launch, n_sets, reps=8):
+        side = torch.cuda.Stream()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(side):
+            for i in range(2):
+                launch(i % n_sets)
+            torch.cuda.synchronize()
+            with torch.cuda.graph(graph, stream=side):
+                for i in range(reps):
+                    launch(i % n_sets)
+        for _ in range(2):
+            graph.replay()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(3):
+            graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / (3 * reps) * 1e3
+
+    def report(name, rows, us, nbytes=None, flops=None):
+        rec = {"kernel": name, "rows": rows, "us": round(us, 1)}
+        if nbytes is not None:
+            rec.update(gbs=round(nbytes / us / 1e3, 1), of_hbm=round(nbytes / us / 1e3 / pk["hbm_gbs"], 3))
+        if flops is not None:
+            rec.update(tflops=round(flops / us / 1e6, 2), of_fma=round(flops / us / 1e6 / fma, 3))
+        print(json.dumps(rec), flush=True)
+
+    for label, lens in (("prompt", [args.prefill_tokens]), ("decode", [1] * args.batch)):
+        T, B = sum(lens), len(lens)
+        c = Ctx()
+        start = [0]
+        for n in lens:
+            start.append(start[-1] + n)
+        c.seq_start = torch.tensor(start, dtype=torch.int32, device=dev)
+        c.tok_seq = torch.repeat_interleave(torch.arange(B, dtype=torch.int32, device=dev), torch.tensor(lens, device=dev)).int()
+        c.slots = torch.arange(B, dtype=torch.int32, device=dev)
+        c.n_seqs, c.max_new = B, max(lens)
+        n_sets = 4 if T > 64 else 24
+        # ---- residual sum + layer norm
+        xs = [torch.randn(T, W, device=dev) for _ in range(n_sets)]
+        ad = [torch.randn(T, W, device=dev).to(dt) for _ in range(n_sets)]
+        wn = torch.ones(W, device=dev).to(dt)
+        y = torch.empty(T, W, dtype=torch.float32, device=dev)
+        us = timed(lambda i: k.add_norm(xs[i], [(ad[i], 0.5)], None, wn, y, 1e-5, True), n_sets)
+        report(f"add_norm ({label})", T, us, nbytes=T * W * (4 + 4 + esz + 4))
+        # ---- short convolution in front of the mixer (float in, element type out), state update included
+        wc = torch.randn(W, 4, device=dev).to(dt)
+        st = torch.zeros(B + 1, 3, W, device=dev)
+        yo = torch.empty(T, W, dtype=dt, device=dev)
+        us = timed(lambda i: k.causal_conv(xs[i], wc, st, c, yo, 4, add_input=True), n_sets)
+        report(f"causal_conv width {W} ({label})", T, us, nbytes=T * W * (4 + esz) + (2 * B * 3 * W * 4 if T == B else 0))
+        # ---- gated delta rule
+        qk = [torch.randn(T, 2 * G * dk, device=dev) for _ in range(n_sets)]
+        vv = [torch.randn(T, H * dv, device=dev) for _ in range(n_sets)]
+        ba = torch.randn(T, 2 * H, device=dev)
+        al, db = torch.zeros(H, device=dev).to(dt), torch.zeros(H, device=dev).to(dt)
+        bd = torch.empty(T, 2 * H + G, device=dev)
+        n_st = 1 if T > 64 else n_sets
+        S = [torch.zeros(B + 1, H, dk, dv, device=dev) for _ in range(n_st)]
+        o = torch.empty(T, H * dv, device=dev)
+        us = timed(lambda i: k.delta_prepare(qk[i], ba, al, db, bd, H, G, dk), n_sets)
+        report(f"delta_prepare ({label})", T, us, nbytes=T * (4 * G * dk * 4))
+        k.delta_prepare(qk[0], ba, al, db, bd, H, G, dk)
+        us = timed(lambda i: k.delta_rule(qk[i], vv[i], bd, S[i % n_st], c, o, H, G, dk, dv), n_sets)
+        report(f"delta_rule heads {H} x {dk} x {dv} ({label})", T, us,
+               nbytes=(T * (2 * G * dk + 2 * H * dv) * 4 + 2 * B * H * dk * dv * 4), flops=7 * T * H * dk * dv)
+        # ---- gated linear recurrence
+        gates = [torch.randn(z["blocks"], T, 2 * bs, device=dev) for _ in range(n_sets)]
+        u = [torch.randn(T, LW, device=dev) for _ in range(n_sets)]
+        yraw = torch.randn(T, LW, device=dev).to(dt)
+        zb = torch.zeros(LW, device=dev).to(dt)
+        Ls = torch.zeros(B + 1, LW, device=dev)
+        out = torch.empty(T, LW, dtype=dt, device=dev)
+        us = timed(lambda i: k.rglru_scan(gates[i], u[i], yraw, zb, zb, zb, zb, Ls, c, out, bs), n_sets)
+        report(f"rglru_scan width {LW} ({label})", T, us, nbytes=T * LW * (8 + 4 + esz + esz))
+        # ---- attention: cache write with value norm, then the kernel for values of another width than keys
+        if dt == torch.bfloat16 or T <= 64:
+            ctxlen = args.context if T == B else T
+            pages = -(-ctxlen // 64)
+            kp = torch.randn(B * pages + 1, AG, 64, hd, device=dev).to(dt)
+            vp = torch.randn(B * pages + 1, AG, 64, vd, device=dev).to(dt)
+            table = torch.arange(B * pages, dtype=torch.int32, device=dev).view(B, pages).contiguous()
+            pos = (torch.arange(T, dtype=torch.int32, device=dev) if T != B else
+                   torch.full((B,), ctxlen - 1, dtype=torch.int32, device=dev))
+            qkv = torch.randn(T, AH * hd + AG * hd + AG * vd, device=dev).to(dt)
+            cs = torch.zeros(ctxlen + 1, hd // 4, 2, device=dev)
+            cs[..., 0] = 1.0
+            us = timed(lambda i: k.kv_store(qkv, pos, c.tok_seq, table, cs, kp, vp, AH, AG, hd, vd, hd // 2, True, 1e-5), 1)
+            report(f"kv_store ({label})", T, us, nbytes=T * (AH * hd + 2 * AG * (hd + vd)) * esz)
+            ao = torch.empty(T, AH * vd, dtype=dt, device=dev)
+            us = timed(lambda i: k.attn_wide_value(qkv, ao, pos, c.tok_seq, table, kp, vp, AH, AG, hd, vd, window, 0.1), 1)
+            keys = sum(min(int(p) + 1, window) for p in pos.tolist())
+            report(f"attn_wide_value keys {hd} values {vd} window {window} ({label})", T, us,
+                   nbytes=(keys * AG * (hd + vd) * esz if T == B else None), flops=2 * keys * AH * (hd + vd))
+    return 0
+
+
 def kernel_alone(args):
     """One decode kernel by itself, as profiles/ quotes it: launched back to back in a CUDA graph over
     inputs that rotate through more bytes than L2 holds, timed with CUDA events; one JSON line per case.
@@ -615,8 +734,9 @@ def main():
     ap.add_argument("--no-shapes", dest="shapes", action="store_false", help="skip the Llama-3.2-1B and Llama-3.1-8B sizes")
     ap.add_argument("--only", default="all", choices=["all", "prefill", "decode"],
                     help="run one part only (a small case to profile); the JSON line then holds that part alone")
-    ap.add_argument("--kernel", default=None, choices=["attn_decode", "gemm_small_m"],
-                    help="time one decode kernel alone at --shape, --batch (and --context) instead of the model")
+    ap.add_argument("--kernel", default=None, choices=["attn_decode", "gemm_small_m", "sequence"],
+                    help="time one decode kernel alone at --shape, --batch (and --context) instead of the model; 'sequence': "
+                         "the kernels of the mixers with state at --design-sizes, for a prompt and for a decode step")
     ap.add_argument("--design", default=None, choices=["sozilix"],
                     help="measure this design's prompt step and decoding at a few real layer sizes beside the Llama decoder "
                          "of equal size (--prefill-tokens, --batch, --context, --steps, --dtype, --only apply) instead of the "
@@ -631,6 +751,8 @@ def main():
         print(json.dumps({"error": "this library runs on one GPU; bench.py measures N=1 only", "n_gpus": args.gpus}))
         return 2
     args.warmup = max(3, args.warmup)
+    if args.kernel == "sequence":
+        return sequence_kernels_alone(args)
     if args.kernel is not None:
         return kernel_alone(args)
     if args.design is not None:

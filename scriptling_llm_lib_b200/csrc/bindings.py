@@ -650,14 +650,22 @@ class SequenceKernels:
                "attn_wide_value")
 
     def delta_prepare(self, qk, ba, a_log, dt_bias, bd, n_heads, n_kv, dk):
+        """qk float32 rows [G dk | G dk]: queries and keys become unit vectors (queries times dk^-1/2) in place;
+        bd float32 [T, 2H + G] receives beta = sigmoid(ba[:, :H]), decay = exp(-exp(a_log) softplus(ba[:, H:2H] +
+        dt_bias)) and k . q per query/key head."""
+        if tuple(bd.shape) != (qk.shape[0], 2 * n_heads + n_kv):
+            raise KernelError(f"delta_prepare: bd is {tuple(bd.shape)}, expected {(qk.shape[0], 2 * n_heads + n_kv)}")
         _check(self._fn("delta_prepare")(self._view(qk, "qk"), c_int(qk.stride(0)), self._view(ba, "ba"), c_int(ba.stride(0)),
                                          _ptr(a_log, None, "a_log"), _ptr(dt_bias, None, "dt_bias"),
                                          c_int(self._flag(a_log, "a_log")), _ptr(bd, torch.float32, "bd"), c_int(qk.shape[0]),
                                          c_int(n_heads), c_int(n_kv), c_int(dk), _stream()), "delta_prepare")
 
     def delta_rule(self, qk, v, bd, state, ctx, o, n_heads, n_kv, dk, dv):
-        """qk float32 rows [G dk queries | G dk keys] (unit vectors), v float32 [T, H dv], bd float32 [T, 2H]
-        (beta | decay), state float32 [slots, H, dk, dv] (read and advanced), o float32 [T, H dv]."""
+        """qk float32 rows [G dk queries | G dk keys] (unit vectors), v float32 [T, H dv], bd float32 [T, 2H + G]
+        (beta | decay | k . q, as `delta_prepare` leaves them), state float32 [slots, H, dk, dv] (read and
+        advanced), o float32 [T, H dv]."""
+        if tuple(bd.shape) != (qk.shape[0], 2 * n_heads + n_kv):
+            raise KernelError(f"delta_rule: bd is {tuple(bd.shape)}, expected {(qk.shape[0], 2 * n_heads + n_kv)}")
         if qk.dtype != torch.float32 or v.dtype != torch.float32 or tuple(state.shape[1:]) != (n_heads, dk, dv):
             raise KernelError("delta_rule works on float32 queries, keys, values and state [slots, heads, dk, dv]")
         _check(self._fn("delta_rule")(self._view(qk, "qk"), c_int(qk.stride(0)), self._view(v, "v"), c_int(v.stride(0)),

@@ -18,6 +18,16 @@ template <typename A> __device__ __forceinline__ void st_flag(void* p, int is_f3
   if (is_f32) ((float*)p)[i] = v;
   else ((A*)p)[i] = from_f32<A>(v);
 }
+template <typename A> __device__ __forceinline__ float4 ld4_flag(const void* p, int is_f32, size_t i) {
+  return is_f32 ? ld4((const float*)p + i) : ld4((const A*)p + i);
+}
+template <typename A> __device__ __forceinline__ void st4_flag(void* p, int is_f32, size_t i, float4 v) {
+  if (is_f32) st4((float*)p + i, v);
+  else st4((A*)p + i, v);
+}
+__device__ __forceinline__ float4 ld4_w(const void* w, int is_f32, size_t i) {
+  return is_f32 ? ld4((const float*)w + i) : ld4((const bf16*)w + i);
+}
 __device__ __forceinline__ float sigmoid_f(float z) { return 1.0f / (1.0f + expf(-z)); }
 __device__ __forceinline__ float silu_f(float z) { return z / (1.0f + expf(-z)); }
 __device__ __forceinline__ float softplus_f(float z) { return z > 20.0f ? z : log1pf(expf(z)); }
@@ -39,14 +49,44 @@ struct SeqAddends {
 template <typename A>
 __global__ void add_norm_kernel(float* __restrict__ x, SeqAddends ad, const int* __restrict__ rows,
                                 const void* __restrict__ w, int w_f32, void* __restrict__ y, int y_f32, int d, float eps,
-                                int center) {
-  extern __shared__ float sm_row[];
+                                int center, int vec) {
+  extern __shared__ __align__(16) float sm_row[];
   __shared__ float red[32];
   int r = blockIdx.x;
   size_t in = rows ? (size_t)rows[r] : (size_t)r;
   float* xr = x + in * d;
   bool update = rows == nullptr && ad.n > 0;
   float s = 0.f;
+  if (vec) {                                    // four elements per access: d, every row and the weight 16-byte aligned
+    for (int j = threadIdx.x * 4; j < d; j += blockDim.x * 4) {
+      float4 v = *(const float4*)(xr + j);
+      for (int a = 0; a < ad.n; a++) {
+        float4 t = ld4_flag<A>(ad.p[a], ad.is_f32[a], in * d + j);
+        float c = ad.coef[a];
+        v.x += c * t.x; v.y += c * t.y; v.z += c * t.z; v.w += c * t.w;
+      }
+      *(float4*)(sm_row + j) = v;
+      if (update) *(float4*)(xr + j) = v;
+      s += (v.x + v.y) + (v.z + v.w);
+    }
+    float mean = 0.f;
+    if (center) mean = block_sum(s, red) / (float)d;
+    float ss = 0.f;
+    for (int j = threadIdx.x * 4; j < d; j += blockDim.x * 4) {
+      float4 v = *(const float4*)(sm_row + j);
+      float a = v.x - mean, b = v.y - mean, c = v.z - mean, e = v.w - mean;
+      ss += (a * a + b * b) + (c * c + e * e);
+    }
+    ss = block_sum(ss, red);
+    float inv = 1.0f / sqrtf(ss / (float)d + eps);
+    for (int j = threadIdx.x * 4; j < d; j += blockDim.x * 4) {
+      float4 v = *(const float4*)(sm_row + j);
+      float4 wv = ld4_w(w, w_f32, j);
+      st4_flag<A>(y, y_f32, (size_t)r * d + j, make_float4(((v.x - mean) * inv) * wv.x, ((v.y - mean) * inv) * wv.y,
+                                                            ((v.z - mean) * inv) * wv.z, ((v.w - mean) * inv) * wv.w));
+    }
+    return;
+  }
   for (int j = threadIdx.x; j < d; j += blockDim.x) {
     float v = xr[j];
     for (int a = 0; a < ad.n; a++) v += ad.coef[a] * ld_flag<A>(ad.p[a], ad.is_f32[a], in * d + j);
@@ -107,6 +147,44 @@ __global__ void causal_conv_kernel(ConvArgs p) {
   if (p.act == 1) acc = silu_f(acc);
   st_flag<A>(p.y, p.y_f32, (size_t)t * p.ldy + c, acc);
   if (p.y2) ((A*)p.y2)[(size_t)t * p.ldy2 + c] = from_f32<A>(acc);
+}
+
+// The same, four neighbouring channels per thread with 16-byte (float) or 8-byte accesses: C, the row strides
+// and the buffers' starts are multiples of four elements.
+template <typename A>
+__global__ void causal_conv_vec_kernel(ConvArgs p) {
+  int t = blockIdx.x;
+  int c = (blockIdx.y * blockDim.x + threadIdx.x) * 4;
+  if (c >= p.C) return;
+  int b = p.tok_seq[t];
+  int first = p.seq_start[b];
+  int hist = p.taps - 1;
+  const float* st = p.state + (size_t)p.slots[b] * hist * p.C;
+  float4 ib = p.in_bias ? ld4_w(p.in_bias, p.b_f32, c) : make_float4(0.f, 0.f, 0.f, 0.f);
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f), cur = acc;
+  for (int j = 0; j < p.taps; j++) {
+    int s = t - hist + j;
+    float4 v;
+    if (s >= first) {
+      v = ld4_flag<A>(p.x, p.x_f32, (size_t)s * p.ldx + c);
+      v.x += ib.x; v.y += ib.y; v.z += ib.z; v.w += ib.w;
+    } else {
+      v = *(const float4*)(st + (size_t)(hist + (s - first)) * p.C + c);
+    }
+    acc.x += load_w(p.w, p.w_f32, (size_t)c * p.taps + j) * v.x;
+    acc.y += load_w(p.w, p.w_f32, (size_t)(c + 1) * p.taps + j) * v.y;
+    acc.z += load_w(p.w, p.w_f32, (size_t)(c + 2) * p.taps + j) * v.z;
+    acc.w += load_w(p.w, p.w_f32, (size_t)(c + 3) * p.taps + j) * v.w;
+    cur = v;
+  }
+  if (p.out_bias) {
+    float4 ob = ld4_w(p.out_bias, p.b_f32, c);
+    acc.x += ob.x; acc.y += ob.y; acc.z += ob.z; acc.w += ob.w;
+  }
+  if (p.add_input) { acc.x += cur.x; acc.y += cur.y; acc.z += cur.z; acc.w += cur.w; }
+  if (p.act == 1) { acc.x = silu_f(acc.x); acc.y = silu_f(acc.y); acc.z = silu_f(acc.z); acc.w = silu_f(acc.w); }
+  st4_flag<A>(p.y, p.y_f32, (size_t)t * p.ldy + c, acc);
+  if (p.y2) st4((A*)p.y2 + (size_t)t * p.ldy2 + c, acc);
 }
 
 // After the convolution of a step: the state becomes the last taps - 1 inputs of [state | step's rows].
@@ -263,7 +341,8 @@ __global__ void __launch_bounds__(128) attn_wide_value_kernel(const A* __restric
 // Before the recurrence, per row: queries and keys (float, [G heads of dk] each, at qk and qk + G * dk of a row
 // of ld_qk floats) become unit vectors x / sqrt(sum x^2 + 1e-6), queries times dk^-1/2; ba holds the raw
 // projections [H betas | H decays] of a row (ld_ba floats): beta = sigmoid(b), decay = exp(-exp(A_log) *
-// softplus(a + dt_bias)), written to bd[t][0..H) and bd[t][H..2H).
+// softplus(a + dt_bias)), written to bd[t][0..H) and bd[t][H..2H); bd[t][2H + g] receives k . q of q/k head g
+// (after the scaling), which the recurrence's read-out needs. A row of bd has 2H + G floats.
 template <typename A>
 __global__ void delta_prepare_kernel(float* __restrict__ qk, int ld_qk, const float* __restrict__ ba, int ld_ba,
                                      const void* __restrict__ a_log, const void* __restrict__ dt_bias, int w_f32,
@@ -271,105 +350,173 @@ __global__ void delta_prepare_kernel(float* __restrict__ qk, int ld_qk, const fl
   int t = blockIdx.x;
   int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
   float qmult = rsqrtf((float)dk);
-  for (int hh = wid; hh < 2 * G; hh += nw) {
-    float* v = qk + (size_t)t * ld_qk + (size_t)hh * dk;
-    float ss = 0.f;
-    for (int j = lane; j < dk; j += 32) ss += v[j] * v[j];
-    ss = warp_sum(ss);
-    float inv = 1.0f / sqrtf(ss + 1e-6f);
-    if (hh < G) inv *= qmult;
-    for (int j = lane; j < dk; j += 32) v[j] *= inv;
+  float* brow = bd + (size_t)t * (2 * H + G);
+  for (int gg = wid; gg < G; gg += nw) {
+    float* qv = qk + (size_t)t * ld_qk + (size_t)gg * dk;
+    float* kv = qv + (size_t)G * dk;
+    float sq = 0.f, sk = 0.f;
+    for (int j = lane; j < dk; j += 32) { sq += qv[j] * qv[j]; sk += kv[j] * kv[j]; }
+    sq = warp_sum(sq);
+    sk = warp_sum(sk);
+    float iq = qmult / sqrtf(sq + 1e-6f), ik = 1.0f / sqrtf(sk + 1e-6f);
+    float kq = 0.f;
+    for (int j = lane; j < dk; j += 32) {
+      float a = qv[j] * iq, b2 = kv[j] * ik;
+      qv[j] = a;
+      kv[j] = b2;
+      kq += a * b2;
+    }
+    kq = warp_sum(kq);
+    if (lane == 0) brow[2 * H + gg] = kq;
   }
   for (int h = threadIdx.x; h < H; h += blockDim.x) {
     const float* r = ba + (size_t)t * ld_ba;
-    bd[(size_t)t * 2 * H + h] = sigmoid_f(r[h]);
+    brow[h] = sigmoid_f(r[h]);
     float dt = softplus_f(r[H + h] + load_w(dt_bias, w_f32, h));
-    bd[(size_t)t * 2 * H + H + h] = expf(-expf(load_w(a_log, w_f32, h)) * dt);
+    brow[H + h] = expf(-expf(load_w(a_log, w_f32, h)) * dt);
   }
 }
 
-// The recurrence itself. One warp per (8 value columns, head, sequence): four lanes share a column j of the
-// head's state S [dk][dv] (row-major in the state tensor [slot][H][dk][dv]); lane r of them keeps the rows
-// 16 m + 4 r + (0..3), m = 0, 1, ..., in registers, and the warp walks the sequence's rows in order:
-//   S *= decay;  u = beta * (v_j - sum_d S[d] k[d]);  S[d] += k[d] u;  o_j = sum_d S[d] q[d]
-// (each sum runs in four partial sums and ends with two shuffles among the four lanes). q and k of a row are
-// staged in shared memory by the warp and read back 16 bytes at a time, the next row's being fetched while
-// this row is worked on. DKR rows per lane (a multiple of 4): dk <= 4 DKR.
+// The recurrence itself. A block of two computing warps per (8 value columns, head, sequence): eight lanes share a
+// column j of the head's state S [dk][dv] (row-major in the state tensor [slot][H][dk][dv]); lane r of them
+// keeps the rows 32 m + 4 r + (0..3), m = 0, 1, ..., in registers, and the block walks the sequence's rows in order:
+//   S *= decay;  u = beta * (v_j - sum_d S[d] k[d]);  S[d] += k[d] u;  o_j = sum_d S[d] q[d].
+// The read-out of the new state is taken from the old one, o_j = decay * sum_d S_old[d] q[d] + u * (k . q) with
+// k . q from the prepare kernel, so both sums run side by side (each in four partial sums, ending with three
+// shuffles among the eight lanes) and a row costs one round of shuffles, not two. What a row brings
+// (q, k, the 8 values, beta, decay, k . q) comes through a ring of DR_RING rows in shared memory filled by
+// asynchronous copies, a batch of DR_BATCH rows ahead of the batch worked on, so the walk waits for memory once, not
+// once per row. A third warp does nothing but send the copies off, so that the two computing warps' instructions are
+// the sums alone; two block barriers per batch hand the ring's halves back and forth. DKR rows per lane (a multiple of 4): dk <= 8 DKR. vec: every copy
+// is 16 bytes and aligned.
+#define DR_RING 16
+#define DR_BATCH 8      // rows per barrier; two batches fill the ring
+#define DR_THREADS 64
+__device__ __forceinline__ void cp_async4(void* dst, const void* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async16(void* dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
 template <int DKR>
-__global__ void __launch_bounds__(32) delta_rule_kernel(const float* __restrict__ qk, int ld_qk, const float* __restrict__ v,
-                                                         int ld_v, const float* __restrict__ bd, float* __restrict__ state,
-                                                         const int* __restrict__ seq_start, const int* __restrict__ slots,
-                                                         float* __restrict__ o, int H, int G, int dk, int dv) {
+__global__ void __launch_bounds__(DR_THREADS + 32) delta_rule_kernel(const float* __restrict__ qk, int ld_qk,
+                                                                      const float* __restrict__ v, int ld_v,
+                                                                      const float* __restrict__ bd, float* __restrict__ state,
+                                                                      const int* __restrict__ seq_start,
+                                                                      const int* __restrict__ slots, float* __restrict__ o, int H,
+                                                                      int G, int dk, int dv, int vec) {
   static_assert(DKR % 4 == 0, "a lane keeps whole quads of rows");
-  constexpr int DKP = 4 * DKR;                  // key width with padding (zeros)
-  constexpr int NL = (DKP + 31) / 32;           // staged values per lane
+  constexpr int DKP = 8 * DKR;                  // key width with padding (zeros)
   constexpr int NQ = DKR / 4;                   // quads per lane
-  __shared__ __align__(16) float sq[2][DKP], sk[2][DKP];
-  int lane = threadIdx.x, r = lane & 3;
-  int j = blockIdx.x * 8 + (lane >> 2), h = blockIdx.y, b = blockIdx.z;
+  constexpr int ROW = 2 * DKP + 12;             // floats of a ring entry: q | k | 8 values | beta, decay, k.q | 1 unused
+  extern __shared__ __align__(16) float ring[];
+  int tid = threadIdx.x;
+  int j0 = blockIdx.x * 8, h = blockIdx.y, b = blockIdx.z;
   int g = h / (H / G);
+  for (int i = tid; i < DR_RING * ROW; i += DR_THREADS + 32) ring[i] = 0.f;     // the padding stays zero: copies never touch it
+  __syncthreads();
+  int t0 = seq_start[b], t1 = seq_start[b + 1];
+  int batches = (t1 - t0 + DR_BATCH - 1) / DR_BATCH;
+  // Both kinds of warps pass the same two barriers per batch: (A) the batch before is done with, its half of the
+  // ring may be filled again; (B) this batch has landed.
+  if (tid >= DR_THREADS) {
+    // ---- the copying warp: batch i + 1 is on its way while batch i is worked on
+    int lane = tid - DR_THREADS;
+    const int bd_row = 2 * H + G, k_off = G * dk;
+    const float* src_q = qk + (size_t)t0 * ld_qk + (size_t)g * dk;
+    const float* src_v = v + (size_t)t0 * ld_v + (size_t)h * dv + j0;
+    const float* src_bd = bd + (size_t)t0 * bd_row;
+    int t_next = t0;
+    auto fill_batch = [&](int half) {
+      for (int i = 0; i < DR_BATCH && t_next < t1; i++, t_next++) {
+        float* e = ring + (half * DR_BATCH + i) * ROW;
+        if (vec) {
+          for (int d = 4 * lane; d < dk; d += 128) {
+            cp_async16(e + d, src_q + d);
+            cp_async16(e + DKP + d, src_q + k_off + d);
+          }
+          if (lane < 2 && j0 + 4 * lane < dv) cp_async16(e + 2 * DKP + 4 * lane, src_v + 4 * lane);
+        } else {
+          for (int d = lane; d < dk; d += 32) {
+            cp_async4(e + d, src_q + d);
+            cp_async4(e + DKP + d, src_q + k_off + d);
+          }
+          if (lane < 8 && j0 + lane < dv) cp_async4(e + 2 * DKP + lane, src_v + lane);
+        }
+        if (lane == 8) cp_async4(e + 2 * DKP + 8, src_bd + h);
+        if (lane == 9) cp_async4(e + 2 * DKP + 9, src_bd + H + h);
+        if (lane == 10) cp_async4(e + 2 * DKP + 10, src_bd + 2 * H + g);
+        src_q += ld_qk;
+        src_v += ld_v;
+        src_bd += bd_row;
+      }
+      cp_async_commit();
+    };
+    fill_batch(0);
+    for (int i = 0; i < batches; i++) {
+      __syncthreads();                          // (A)
+      cp_async_wait<0>();                       // batch i, sent off one batch ago
+      __syncthreads();                          // (B)
+      fill_batch((i + 1) & 1);
+    }
+    cp_async_wait<0>();
+    return;
+  }
+  // ---- the two computing warps
+  int r = tid & 7, col = tid >> 3, j = j0 + col;
   bool live = j < dv;
   float* Sg = state + (((size_t)slots[b] * H + h) * dk) * dv + j;
   float S[DKR];
 #pragma unroll
   for (int i = 0; i < DKR; i++) {
-    int d = 16 * (i >> 2) + 4 * r + (i & 3);
+    int d = 32 * (i >> 2) + 4 * r + (i & 3);
     S[i] = (live && d < dk) ? Sg[(size_t)d * dv] : 0.f;
   }
-  int t0 = seq_start[b], t1 = seq_start[b + 1];
-  float rq[NL], rk[NL], beta = 0.f, decay = 0.f, vj = 0.f;
-  auto fetch = [&](int t) {
-    const float* qr = qk + (size_t)t * ld_qk + (size_t)g * dk;
-    const float* kr = qr + (size_t)G * dk;
+  float* dst_o = o + (size_t)t0 * H * dv + (size_t)h * dv + j;
+  const int o_step = H * dv;
+  for (int ib = 0; ib < batches; ib++) {
+    __syncthreads();                            // (A)
+    __syncthreads();                            // (B)
+    int n = min(DR_BATCH, t1 - t0 - ib * DR_BATCH);
+    const float* e = ring + (ib & 1) * DR_BATCH * ROW;
+    for (int i = 0; i < n; i++, e += ROW) {
+      float de = e[2 * DKP + 9], be = e[2 * DKP + 8], vv = e[2 * DKP + col], kdotq = e[2 * DKP + 10];
+      float4 kk[NQ], qq[NQ];
 #pragma unroll
-    for (int i = 0; i < NL; i++) {
-      int d = lane + 32 * i;
-      rq[i] = d < dk ? qr[d] : 0.f;
-      rk[i] = d < dk ? kr[d] : 0.f;
-    }
-    beta = bd[(size_t)t * 2 * H + h];
-    decay = bd[(size_t)t * 2 * H + H + h];
-    vj = live ? v[(size_t)t * ld_v + (size_t)h * dv + j] : 0.f;
-  };
-  if (t0 < t1) fetch(t0);
-  for (int t = t0; t < t1; t++) {
-    int buf = (t - t0) & 1;
+      for (int m = 0; m < NQ; m++) {
+        kk[m] = *(const float4*)&e[DKP + 32 * m + 4 * r];
+        qq[m] = *(const float4*)&e[32 * m + 4 * r];
+      }
+      float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f, c0 = 0.f, c1 = 0.f, c2 = 0.f, c3 = 0.f;
 #pragma unroll
-    for (int i = 0; i < NL; i++) {
-      int d = lane + 32 * i;
-      if (d < DKP) { sq[buf][d] = rq[i]; sk[buf][d] = rk[i]; }
-    }
-    float be = beta, de = decay, vv = vj;
-    __syncwarp();
-    if (t + 1 < t1) fetch(t + 1);
-    float4 kq[NQ];
-    float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
+      for (int m = 0; m < NQ; m++) {
+        a0 += S[4 * m] * kk[m].x; a1 += S[4 * m + 1] * kk[m].y; a2 += S[4 * m + 2] * kk[m].z; a3 += S[4 * m + 3] * kk[m].w;
+        c0 += S[4 * m] * qq[m].x; c1 += S[4 * m + 1] * qq[m].y; c2 += S[4 * m + 2] * qq[m].z; c3 += S[4 * m + 3] * qq[m].w;
+      }
+      float sk = (a0 + a1) + (a2 + a3), sq = (c0 + c1) + (c2 + c3);      // of the old state: S_old^T k and S_old^T q
 #pragma unroll
-    for (int m = 0; m < NQ; m++) {
-      kq[m] = *(const float4*)&sk[buf][16 * m + 4 * r];
-      S[4 * m] *= de; S[4 * m + 1] *= de; S[4 * m + 2] *= de; S[4 * m + 3] *= de;
-      d0 += S[4 * m] * kq[m].x; d1 += S[4 * m + 1] * kq[m].y; d2 += S[4 * m + 2] * kq[m].z; d3 += S[4 * m + 3] * kq[m].w;
-    }
-    float dot = (d0 + d1) + (d2 + d3);
-    dot += __shfl_xor_sync(0xffffffffu, dot, 1);
-    dot += __shfl_xor_sync(0xffffffffu, dot, 2);
-    float u = be * (vv - dot);
-    d0 = d1 = d2 = d3 = 0.f;
+      for (int w = 1; w < 8; w <<= 1) {
+        sk += __shfl_xor_sync(0xffffffffu, sk, w);
+        sq += __shfl_xor_sync(0xffffffffu, sq, w);
+      }
+      float u = be * (vv - de * sk);
+      float oj = de * sq + u * kdotq;
 #pragma unroll
-    for (int m = 0; m < NQ; m++) {
-      float4 qq = *(const float4*)&sq[buf][16 * m + 4 * r];
-      S[4 * m] += kq[m].x * u; S[4 * m + 1] += kq[m].y * u; S[4 * m + 2] += kq[m].z * u; S[4 * m + 3] += kq[m].w * u;
-      d0 += S[4 * m] * qq.x; d1 += S[4 * m + 1] * qq.y; d2 += S[4 * m + 2] * qq.z; d3 += S[4 * m + 3] * qq.w;
+      for (int m = 0; m < NQ; m++) {
+        S[4 * m] = de * S[4 * m] + kk[m].x * u; S[4 * m + 1] = de * S[4 * m + 1] + kk[m].y * u;
+        S[4 * m + 2] = de * S[4 * m + 2] + kk[m].z * u; S[4 * m + 3] = de * S[4 * m + 3] + kk[m].w * u;
+      }
+      if (live && r == 0) *dst_o = oj;
+      dst_o += o_step;
     }
-    float oj = (d0 + d1) + (d2 + d3);
-    oj += __shfl_xor_sync(0xffffffffu, oj, 1);
-    oj += __shfl_xor_sync(0xffffffffu, oj, 2);
-    if (live && r == 0) o[(size_t)t * H * dv + (size_t)h * dv + j] = oj;
   }
   if (live) {
 #pragma unroll
     for (int i = 0; i < DKR; i++) {
-      int d = 16 * (i >> 2) + 4 * r + (i & 3);
+      int d = 32 * (i >> 2) + 4 * r + (i & 3);
       if (d < dk) Sg[(size_t)d * dv] = S[i];
     }
   }
@@ -454,7 +601,7 @@ __global__ void rglru_scan_kernel(LruArgs p) {
 // S_end = prod * S_start + end. (2) A thread per (sequence, channel) carries the state from piece to piece
 // and leaves every piece's S_start (the sequence's state is advanced here). (3) A thread per (piece, channel)
 // runs its piece again from S_start and writes the rows. `pieces` = most pieces of any sequence.
-#define LRU_PIECE 32
+#define LRU_PIECE 16
 template <typename A>
 __global__ void rglru_piece_kernel(LruArgs p, float* __restrict__ prod, float* __restrict__ end, int pieces) {
   int b = blockIdx.x / pieces, k = blockIdx.x % pieces;
@@ -481,11 +628,21 @@ __global__ void rglru_carry_kernel(LruArgs p, const float* __restrict__ prod, fl
   float S = *sp_state;
   int n = p.seq_start[b + 1] - p.seq_start[b];
   int used = (n + LRU_PIECE - 1) / LRU_PIECE;
-  for (int k = 0; k < used; k++) {
-    size_t at = ((size_t)b * pieces + k) * p.W + c;
-    float next = prod[at] * S + end[at];
-    end[at] = S;                                // from here on: the piece's start value
-    S = next;
+  for (int k0 = 0; k0 < used; k0 += 8) {        // eight pieces' terms fetched together, then chained
+    float P[8], E[8];
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+      size_t at = ((size_t)b * pieces + min(k0 + i, used - 1)) * p.W + c;
+      P[i] = prod[at];
+      E[i] = end[at];
+    }
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+      if (k0 + i < used) {
+        end[((size_t)b * pieces + k0 + i) * p.W + c] = S;      // from here on: the piece's start value
+        S = P[i] * S + E[i];
+      }
+    }
   }
   *sp_state = S;
 }

@@ -76,7 +76,7 @@ class GatedDeltaRule(Mixer):
         ba = self.small.forward(x, ctx, out_dtype=torch.float32)                # [T, beta | decay (| padding)] float32
         n_conv = 2 * self.qk_width + self.v_width
         qkv = self.conv.forward(proj[:, :n_conv], st.get("conv"), ctx, torch.float32)       # float32 [T, q | k | v]
-        bd = torch.empty((T, 2 * self.H), dtype=torch.float32, device=x.device)
+        bd = torch.empty((T, 2 * self.H + self.G), dtype=torch.float32, device=x.device)    # beta | decay | k . q
         k.delta_prepare(qkv[:, :2 * self.qk_width], ba, self.a_log, self.dt_bias, bd, self.H, self.G, self.dk)
         o = torch.empty((T, self.v_width), dtype=torch.float32, device=x.device)
         k.delta_rule(qkv[:, :2 * self.qk_width], qkv[:, 2 * self.qk_width:], bd, st["S"], ctx, o, self.H, self.G, self.dk, self.dv)

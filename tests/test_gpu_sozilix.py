@@ -418,7 +418,8 @@ def test_the_delta_rule_forgets_by_its_decay_and_overwrites_along_a_key():
     qk = torch.stack([torch.cat([e0, e0]), torch.cat([e0, e1]), torch.cat([e0, e0]), torch.cat([e1, e1])]).to(dev).contiguous()
     g = torch.Generator().manual_seed(0)
     v = torch.randn(4, H * dv, generator=g).to(dev)
-    bd = torch.tensor([[1, 1, 1, 1], [1, 1, 0.5, 0.25], [1, 1, 1, 1], [0, 0, 1, 1]], dtype=torch.float32, device=dev)  # beta | decay
+    # beta | decay | k . q of the row
+    bd = torch.tensor([[1, 1, 1, 1, 1], [1, 1, 0.5, 0.25, 0], [1, 1, 1, 1, 1], [0, 0, 1, 1, 1]], dtype=torch.float32, device=dev)
     state = torch.zeros(3, H, dk, dv, device=dev)
     o = torch.empty(4, H * dv, device=dev)
     k.delta_rule(qk, v, bd, state, _Ctx([4], [2], dev), o, H, G, dk, dv)
