@@ -266,67 +266,123 @@ __global__ void kv_store_kernel(A* __restrict__ qkv, int ld, const int* __restri
 }
 
 // ------------------------------------------------------------------ attention, keys of width hd, values of width vd
-// One block of four warps per (row, query head). A warp takes every fourth visible key: the score is a sum
-// over the lanes, the softmax runs on line (a running maximum and sum per warp), and each lane keeps vd / 32
-// sums of weighted values; the four warps are merged at the end. Row t sees the keys at positions
-// max(0, pos - window + 1) .. pos of its own sequence (window 0: all of them).
-template <typename A, int NV>
+// One warp per (row, query head), four to a block with the heads running fastest, so that the warps of a block
+// mostly read the same key/value head. The warp takes its visible keys 32 at a time: a lane scores one key (its
+// row of the cache against the query in shared memory), the running maximum and sum of the softmax are updated
+// once per 32 keys, and the weighted values are summed with a lane per value column (vd / 32 sums a lane), the
+// weights passed round by shuffles. Row t sees the keys at positions max(0, pos - window + 1) .. pos of its own
+// sequence (window 0: all of them). vec8: key rows can be read 8 elements (16 bytes of bfloat16, 32 of float) at a time.
+// WPI warps per (row, head): 1, or 4 for steps of few rows (a decode step), where the four take every fourth
+// group of 32 keys and are merged through shared memory at the end.
+template <typename A, int NV, int WPI>
 __global__ void __launch_bounds__(128) attn_wide_value_kernel(const A* __restrict__ q, int q_ld, A* __restrict__ out, int out_ld,
                                                               const int* __restrict__ tok_pos, const int* __restrict__ tok_seq,
                                                               const int* __restrict__ block_table, int max_pages,
-                                                              const A* __restrict__ kpages, const A* __restrict__ vpages, int H,
-                                                              int G, int hd, int vd, int window, float scale) {
-  extern __shared__ float sm_att[];             // q[hd], then per warp: acc[32 * NV], m, l
-  int t = blockIdx.x, h = blockIdx.y;
+                                                              const A* __restrict__ kpages, const A* __restrict__ vpages, int T,
+                                                              int H, int G, int hd, int vd, int window, float scale, int vec8) {
+  extern __shared__ __align__(16) float sm_att[];            // 4 / WPI queries of hd floats; WPI == 4: then 4 x (32 NV + 2) to merge
   int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  size_t item = (size_t)blockIdx.x * (4 / WPI) + wid / WPI;
+  int sub = wid % WPI;
+  bool have = item < (size_t)T * H;
+  if (!have && WPI == 1) return;
+  if (!have) item = (size_t)T * H - 1;          // WPI == 4: one item a block, so this does not happen; keeps the barrier whole
+  int t = (int)(item / H), h = (int)(item % H);
   int g = h / (H / G);
   int pos = tok_pos[t];
   const int* pages = block_table + (size_t)tok_seq[t] * max_pages;
-  float* qs = sm_att;
-  for (int j = threadIdx.x; j < hd; j += blockDim.x) qs[j] = to_f32(q[(size_t)t * q_ld + (size_t)h * hd + j]);
-  __syncthreads();
+  float* qs = sm_att + (size_t)(wid / WPI) * hd;
+  if (WPI == 1) {
+    for (int j = lane; j < hd; j += 32) qs[j] = to_f32(q[(size_t)t * q_ld + (size_t)h * hd + j]) * scale;
+    __syncwarp();
+  } else {
+    for (int j = threadIdx.x; j < hd; j += 128) qs[j] = to_f32(q[(size_t)t * q_ld + (size_t)h * hd + j]) * scale;
+    __syncthreads();
+  }
   int lo = window > 0 ? max(0, pos - window + 1) : 0;
   float m = -INFINITY, l = 0.f, acc[NV];
 #pragma unroll
   for (int i = 0; i < NV; i++) acc[i] = 0.f;
-  for (int kp = lo + wid; kp <= pos; kp += 4) {
-    size_t at = ((size_t)pages[kp / SLLM_PAGE] * G + g) * SLLM_PAGE + (kp % SLLM_PAGE);
-    const A* kr = kpages + at * hd;
-    float s = 0.f;
-    for (int j = lane; j < hd; j += 32) s += qs[j] * to_f32(kr[j]);
-    s = warp_sum(s) * scale;
-    float m_new = fmaxf(m, s);
-    float c = expf(m - m_new), e = expf(s - m_new);       // expf(-inf) = 0 on the first key
-    l = l * c + e;
-    const A* vr = vpages + at * vd;
+  for (int base = lo + 32 * sub; base <= pos; base += 32 * WPI) {
+    int kp = base + lane;
+    bool seen = kp <= pos;
+    unsigned at = 0;                            // the key's row in the store: (page * G + g) * PAGE + offset
+    float sc = -INFINITY;
+    if (seen) {
+      at = ((unsigned)pages[kp / SLLM_PAGE] * G + g) * SLLM_PAGE + (kp % SLLM_PAGE);
+      const A* kr = kpages + (size_t)at * hd;
+      float s0 = 0.f, s1 = 0.f;
+      if (vec8) {
+        for (int d = 0; d < hd; d += 8) {
+          F8 kv = ld8(kr + d);
+          s0 += qs[d] * kv.f[0] + qs[d + 2] * kv.f[2] + qs[d + 4] * kv.f[4] + qs[d + 6] * kv.f[6];
+          s1 += qs[d + 1] * kv.f[1] + qs[d + 3] * kv.f[3] + qs[d + 5] * kv.f[5] + qs[d + 7] * kv.f[7];
+        }
+      } else {
+        for (int d = 0; d < hd; d++) s0 += qs[d] * to_f32(kr[d]);
+      }
+      sc = s0 + s1;
+    }
+    float m_new = fmaxf(m, warp_max(sc));
+    float c = expf(m - m_new);                  // expf(-inf) = 0 before the first key
+    float pw = seen ? expf(sc - m_new) : 0.f;
+    l = l * c + warp_sum(pw);
 #pragma unroll
-    for (int i = 0; i < NV; i++) {
-      int j = lane + 32 * i;
-      float v = j < vd ? to_f32(vr[j]) : 0.f;
-      acc[i] = acc[i] * c + e * v;
+    for (int i = 0; i < NV; i++) acc[i] *= c;
+    int n = min(32, pos - base + 1);
+    // UB keys' values asked for together, then summed: eight where few warps run (their loads must overlap one
+    // another), one where the GPU is full of warps (registers are worth more there)
+    constexpr int UB = WPI == 1 ? 1 : 8;
+    for (int j0 = 0; j0 < n; j0 += UB) {
+      float pj[UB], vals[UB][NV];
+#pragma unroll
+      for (int jj = 0; jj < UB; jj++) {
+        int src = min(j0 + jj, n - 1);
+        pj[jj] = j0 + jj < n ? __shfl_sync(0xffffffffu, pw, src) : 0.f;
+        unsigned aj = __shfl_sync(0xffffffffu, at, src);
+        const A* vr = vpages + (size_t)aj * vd;
+#pragma unroll
+        for (int i = 0; i < NV; i++) {
+          int j = lane + 32 * i;
+          vals[jj][i] = j < vd ? to_f32(vr[j]) : 0.f;
+        }
+      }
+#pragma unroll
+      for (int jj = 0; jj < UB; jj++) {
+#pragma unroll
+        for (int i = 0; i < NV; i++) acc[i] += pj[jj] * vals[jj][i];
+      }
     }
     m = m_new;
   }
-  float* wacc = sm_att + hd + (size_t)wid * (32 * NV + 2);
+  if (WPI == 1) {
+    float inv = 1.0f / l;
 #pragma unroll
-  for (int i = 0; i < NV; i++) wacc[lane + 32 * i] = acc[i];
-  if (lane == 0) { wacc[32 * NV] = m; wacc[32 * NV + 1] = l; }
+    for (int i = 0; i < NV; i++) {
+      int j = lane + 32 * i;
+      if (j < vd) out[(size_t)t * out_ld + (size_t)h * vd + j] = from_f32<A>(acc[i] * inv);
+    }
+    return;
+  }
+  float* part = sm_att + hd + (size_t)wid * (32 * NV + 2);
+#pragma unroll
+  for (int i = 0; i < NV; i++) part[lane + 32 * i] = acc[i];
+  if (lane == 0) { part[32 * NV] = m; part[32 * NV + 1] = l; }
   __syncthreads();
-  if (wid == 0) {
+  if (wid == 0 && have) {
     float M = -INFINITY;
     for (int w = 0; w < 4; w++) M = fmaxf(M, sm_att[hd + (size_t)w * (32 * NV + 2) + 32 * NV]);
-    float L = 0.f;
-    float o[NV];
+    float L = 0.f, o[NV];
 #pragma unroll
     for (int i = 0; i < NV; i++) o[i] = 0.f;
-    for (int w = 0; w < 4; w++) {                         // fixed order
-      const float* wa = sm_att + hd + (size_t)w * (32 * NV + 2);
-      float mw = wa[32 * NV];
+    for (int w = 0; w < 4; w++) {               // fixed order
+      const float* pa = sm_att + hd + (size_t)w * (32 * NV + 2);
+      float mw = pa[32 * NV];
       if (mw == -INFINITY) continue;
       float c = expf(mw - M);
-      L += wa[32 * NV + 1] * c;
+      L += pa[32 * NV + 1] * c;
 #pragma unroll
-      for (int i = 0; i < NV; i++) o[i] += wa[lane + 32 * i] * c;
+      for (int i = 0; i < NV; i++) o[i] += pa[lane + 32 * i] * c;
     }
     float inv = 1.0f / L;
 #pragma unroll
