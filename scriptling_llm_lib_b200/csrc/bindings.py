@@ -671,8 +671,8 @@ class SequenceKernels:
         _check(self._fn("delta_rule")(self._view(qk, "qk"), c_int(qk.stride(0)), self._view(v, "v"), c_int(v.stride(0)),
                                       _ptr(bd, torch.float32, "bd"), _ptr(state, torch.float32, "state"),
                                       _ptr(ctx.seq_start, torch.int32, "seq_start"), _ptr(ctx.slots, torch.int32, "slots"),
-                                      _ptr(o, torch.float32, "o"), c_int(ctx.n_seqs), c_int(n_heads), c_int(n_kv), c_int(dk),
-                                      c_int(dv), _stream()), "delta_rule")
+                                      _ptr(o, torch.float32, "o"), c_int(ctx.n_seqs), c_int(max(1, ctx.max_new)), c_int(n_heads),
+                                      c_int(n_kv), c_int(dk), c_int(dv), _stream()), "delta_rule")
 
     def gated_unit_rms(self, o, gate, weight, y, n_heads, dv, eps):
         _check(self._fn("gated_unit_rms")(_ptr(o, torch.float32, "o"), self._view(gate, "gate"), c_int(gate.stride(0)),

@@ -433,21 +433,26 @@ __global__ void delta_prepare_kernel(float* __restrict__ qk, int ld_qk, const fl
   }
 }
 
-// The recurrence itself. A block of two computing warps per (8 value columns, head, sequence): eight lanes share a
-// column j of the head's state S [dk][dv] (row-major in the state tensor [slot][H][dk][dv]); lane r of them
-// keeps the rows 32 m + 4 r + (0..3), m = 0, 1, ..., in registers, and the block walks the sequence's rows in order:
+// The recurrence itself. A block of four computing warps per (8 value columns, head, sequence): DR_LPC = 16 lanes
+// share a column j of the head's state S [dk][dv] (row-major in the state tensor [slot][H][dk][dv]); lane r of
+// them keeps the rows 64 m + 4 r + (0..3), m = 0, 1, ..., in registers, and the block walks the sequence's rows in order:
 //   S *= decay;  u = beta * (v_j - sum_d S[d] k[d]);  S[d] += k[d] u;  o_j = sum_d S[d] q[d].
 // The read-out of the new state is taken from the old one, o_j = decay * sum_d S_old[d] q[d] + u * (k . q) with
-// k . q from the prepare kernel, so both sums run side by side (each in four partial sums, ending with three
-// shuffles among the eight lanes) and a row costs one round of shuffles, not two. What a row brings
+// k . q from the prepare kernel, so both sums run side by side (each in four partial sums, ending with four
+// shuffles among the sixteen lanes) and a row costs one round of shuffles, not two. What a row brings
 // (q, k, the 8 values, beta, decay, k . q) comes through a ring of DR_RING rows in shared memory filled by
 // asynchronous copies, a batch of DR_BATCH rows ahead of the batch worked on, so the walk waits for memory once, not
-// once per row. A third warp does nothing but send the copies off, so that the two computing warps' instructions are
-// the sums alone; two block barriers per batch hand the ring's halves back and forth. DKR rows per lane (a multiple of 4): dk <= 8 DKR. vec: every copy
+// once per row. A third warp does nothing but send the copies off, so that the computing warps' instructions are
+// the sums alone; two block barriers per batch hand the ring's halves back and forth. DKR rows per lane (a multiple of 4): dk <= 16 DKR. vec: every copy
 // is 16 bytes and aligned.
-#define DR_RING 16
+#define DR_NB 4            // batches in the ring
+#define DR_DIRECT_MAX 4    // rows of a sequence in a step up to which the ring is not worth its set-up
+#define DR_RING 32
 #define DR_BATCH 8      // rows per barrier; two batches fill the ring
-#define DR_THREADS 64
+#ifndef DR_LPC
+#define DR_LPC 16          // lanes that share a state column
+#endif
+#define DR_THREADS (8 * DR_LPC)     // computing threads: 8 columns x DR_LPC lanes
 __device__ __forceinline__ void cp_async4(void* dst, const void* src) {
   asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
 }
@@ -463,32 +468,45 @@ __global__ void __launch_bounds__(DR_THREADS + 32) delta_rule_kernel(const float
                                                                       const float* __restrict__ bd, float* __restrict__ state,
                                                                       const int* __restrict__ seq_start,
                                                                       const int* __restrict__ slots, float* __restrict__ o, int H,
-                                                                      int G, int dk, int dv, int vec) {
+                                                                      int G, int dk, int dv, int vec, int ring_rows) {
   static_assert(DKR % 4 == 0, "a lane keeps whole quads of rows");
-  constexpr int DKP = 8 * DKR;                  // key width with padding (zeros)
+  constexpr int DKP = DR_LPC * DKR;             // key width with padding (zeros)
   constexpr int NQ = DKR / 4;                   // quads per lane
   constexpr int ROW = 2 * DKP + 12;             // floats of a ring entry: q | k | 8 values | beta, decay, k.q | 1 unused
   extern __shared__ __align__(16) float ring[];
   int tid = threadIdx.x;
   int j0 = blockIdx.x * 8, h = blockIdx.y, b = blockIdx.z;
   int g = h / (H / G);
-  for (int i = tid; i < DR_RING * ROW; i += DR_THREADS + 32) ring[i] = 0.f;     // the padding stays zero: copies never touch it
+  // The block's slice of the state, dk rows of 8 columns (one 32-byte sector a row), goes through shared memory both
+  // ways so that every access to the state tensor covers whole sectors, whichever lanes keep which rows.
+  float* stage = ring + ring_rows * ROW;        // [dk][9]; ring_rows is DR_RING, or 0 when no sequence of the step needs the ring
+  float* Sblock = state + (((size_t)slots[b] * H + h) * dk) * dv + j0;
+  for (int i = tid; i < dk * 8; i += DR_THREADS + 32) {
+    int d = i >> 3, c = i & 7;
+    stage[d * 9 + c] = j0 + c < dv ? Sblock[(size_t)d * dv + c] : 0.f;
+  }
   __syncthreads();
   int t0 = seq_start[b], t1 = seq_start[b + 1];
+  const bool direct = t1 - t0 <= DR_DIRECT_MAX; // a decode step's one row (or a few): straight from global memory, no ring
+  if (!direct && (dk != DKP || j0 + 8 > dv)) {  // padding that no copy touches must read as zero
+    for (int i = tid; i < DR_RING * ROW; i += DR_THREADS + 32) ring[i] = 0.f;
+    __syncthreads();
+  }
   int batches = (t1 - t0 + DR_BATCH - 1) / DR_BATCH;
   // Both kinds of warps pass the same two barriers per batch: (A) the batch before is done with, its half of the
   // ring may be filled again; (B) this batch has landed.
   if (tid >= DR_THREADS) {
-    // ---- the copying warp: batch i + 1 is on its way while batch i is worked on
+    if (direct) return;
+    // ---- the copying warp: batches i + 1 .. i + DR_NB - 1 are on their way while batch i is worked on
     int lane = tid - DR_THREADS;
     const int bd_row = 2 * H + G, k_off = G * dk;
     const float* src_q = qk + (size_t)t0 * ld_qk + (size_t)g * dk;
     const float* src_v = v + (size_t)t0 * ld_v + (size_t)h * dv + j0;
     const float* src_bd = bd + (size_t)t0 * bd_row;
     int t_next = t0;
-    auto fill_batch = [&](int half) {
+    auto fill_batch = [&](int slot) {
       for (int i = 0; i < DR_BATCH && t_next < t1; i++, t_next++) {
-        float* e = ring + (half * DR_BATCH + i) * ROW;
+        float* e = ring + (slot * DR_BATCH + i) * ROW;
         if (vec) {
           for (int d = 4 * lane; d < dk; d += 128) {
             cp_async16(e + d, src_q + d);
@@ -511,40 +529,46 @@ __global__ void __launch_bounds__(DR_THREADS + 32) delta_rule_kernel(const float
       }
       cp_async_commit();
     };
-    fill_batch(0);
+    for (int i = 0; i < DR_NB - 1; i++) fill_batch(i);          // DR_NB - 1 batches are always on their way
     for (int i = 0; i < batches; i++) {
       __syncthreads();                          // (A)
-      cp_async_wait<0>();                       // batch i, sent off one batch ago
+      cp_async_wait<DR_NB - 2>();               // batch i has landed; the later ones may still be under way
       __syncthreads();                          // (B)
-      fill_batch((i + 1) & 1);
+      fill_batch((i + DR_NB - 1) % DR_NB);      // into the slot batch i - 1 used
     }
     cp_async_wait<0>();
     return;
   }
-  // ---- the two computing warps
-  int r = tid & 7, col = tid >> 3, j = j0 + col;
+  // ---- the computing warps
+  int r = tid & (DR_LPC - 1), col = tid / DR_LPC, j = j0 + col;
   bool live = j < dv;
-  float* Sg = state + (((size_t)slots[b] * H + h) * dk) * dv + j;
   float S[DKR];
 #pragma unroll
   for (int i = 0; i < DKR; i++) {
-    int d = 32 * (i >> 2) + 4 * r + (i & 3);
-    S[i] = (live && d < dk) ? Sg[(size_t)d * dv] : 0.f;
+    int d = 4 * DR_LPC * (i >> 2) + 4 * r + (i & 3);
+    S[i] = d < dk ? stage[d * 9 + col] : 0.f;
   }
   float* dst_o = o + (size_t)t0 * H * dv + (size_t)h * dv + j;
   const int o_step = H * dv;
-  for (int ib = 0; ib < batches; ib++) {
-    __syncthreads();                            // (A)
-    __syncthreads();                            // (B)
-    int n = min(DR_BATCH, t1 - t0 - ib * DR_BATCH);
-    const float* e = ring + (ib & 1) * DR_BATCH * ROW;
-    for (int i = 0; i < n; i++, e += ROW) {
-      float de = e[2 * DKP + 9], be = e[2 * DKP + 8], vv = e[2 * DKP + col], kdotq = e[2 * DKP + 10];
+  if (direct) {
+    const int bd_row = 2 * H + G;
+    for (int t = t0; t < t1; t++) {
+      const float* gq = qk + (size_t)t * ld_qk + (size_t)g * dk;
+      const float* gk = gq + (size_t)G * dk;
+      const float* gb = bd + (size_t)t * bd_row;
+      float de = gb[H + h], be = gb[h], kdotq = gb[2 * H + g];
+      float vv = live ? v[(size_t)t * ld_v + (size_t)h * dv + j] : 0.f;
       float4 kk[NQ], qq[NQ];
 #pragma unroll
       for (int m = 0; m < NQ; m++) {
-        kk[m] = *(const float4*)&e[DKP + 32 * m + 4 * r];
-        qq[m] = *(const float4*)&e[32 * m + 4 * r];
+        int d = 4 * DR_LPC * m + 4 * r;
+        if (vec) {
+          kk[m] = d < dk ? *(const float4*)(gk + d) : make_float4(0.f, 0.f, 0.f, 0.f);
+          qq[m] = d < dk ? *(const float4*)(gq + d) : make_float4(0.f, 0.f, 0.f, 0.f);
+        } else {
+          kk[m] = make_float4(d < dk ? gk[d] : 0.f, d + 1 < dk ? gk[d + 1] : 0.f, d + 2 < dk ? gk[d + 2] : 0.f, d + 3 < dk ? gk[d + 3] : 0.f);
+          qq[m] = make_float4(d < dk ? gq[d] : 0.f, d + 1 < dk ? gq[d + 1] : 0.f, d + 2 < dk ? gq[d + 2] : 0.f, d + 3 < dk ? gq[d + 3] : 0.f);
+        }
       }
       float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f, c0 = 0.f, c1 = 0.f, c2 = 0.f, c3 = 0.f;
 #pragma unroll
@@ -552,9 +576,9 @@ __global__ void __launch_bounds__(DR_THREADS + 32) delta_rule_kernel(const float
         a0 += S[4 * m] * kk[m].x; a1 += S[4 * m + 1] * kk[m].y; a2 += S[4 * m + 2] * kk[m].z; a3 += S[4 * m + 3] * kk[m].w;
         c0 += S[4 * m] * qq[m].x; c1 += S[4 * m + 1] * qq[m].y; c2 += S[4 * m + 2] * qq[m].z; c3 += S[4 * m + 3] * qq[m].w;
       }
-      float sk = (a0 + a1) + (a2 + a3), sq = (c0 + c1) + (c2 + c3);      // of the old state: S_old^T k and S_old^T q
+      float sk = (a0 + a1) + (a2 + a3), sq = (c0 + c1) + (c2 + c3);
 #pragma unroll
-      for (int w = 1; w < 8; w <<= 1) {
+      for (int w = 1; w < DR_LPC; w <<= 1) {
         sk += __shfl_xor_sync(0xffffffffu, sk, w);
         sq += __shfl_xor_sync(0xffffffffu, sq, w);
       }
@@ -569,12 +593,51 @@ __global__ void __launch_bounds__(DR_THREADS + 32) delta_rule_kernel(const float
       dst_o += o_step;
     }
   }
-  if (live) {
+  for (int ib = 0; ib < (direct ? 0 : batches); ib++) {
+    __syncthreads();                            // (A)
+    __syncthreads();                            // (B)
+    int n = min(DR_BATCH, t1 - t0 - ib * DR_BATCH);
+    const float* e = ring + (ib % DR_NB) * DR_BATCH * ROW;
+    for (int i = 0; i < n; i++, e += ROW) {
+      float de = e[2 * DKP + 9], be = e[2 * DKP + 8], vv = e[2 * DKP + col], kdotq = e[2 * DKP + 10];
+      float4 kk[NQ], qq[NQ];
 #pragma unroll
-    for (int i = 0; i < DKR; i++) {
-      int d = 32 * (i >> 2) + 4 * r + (i & 3);
-      if (d < dk) Sg[(size_t)d * dv] = S[i];
+      for (int m = 0; m < NQ; m++) {
+        kk[m] = *(const float4*)&e[DKP + 4 * DR_LPC * m + 4 * r];
+        qq[m] = *(const float4*)&e[4 * DR_LPC * m + 4 * r];
+      }
+      float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f, c0 = 0.f, c1 = 0.f, c2 = 0.f, c3 = 0.f;
+#pragma unroll
+      for (int m = 0; m < NQ; m++) {
+        a0 += S[4 * m] * kk[m].x; a1 += S[4 * m + 1] * kk[m].y; a2 += S[4 * m + 2] * kk[m].z; a3 += S[4 * m + 3] * kk[m].w;
+        c0 += S[4 * m] * qq[m].x; c1 += S[4 * m + 1] * qq[m].y; c2 += S[4 * m + 2] * qq[m].z; c3 += S[4 * m + 3] * qq[m].w;
+      }
+      float sk = (a0 + a1) + (a2 + a3), sq = (c0 + c1) + (c2 + c3);      // of the old state: S_old^T k and S_old^T q
+#pragma unroll
+      for (int w = 1; w < DR_LPC; w <<= 1) {
+        sk += __shfl_xor_sync(0xffffffffu, sk, w);
+        sq += __shfl_xor_sync(0xffffffffu, sq, w);
+      }
+      float u = be * (vv - de * sk);
+      float oj = de * sq + u * kdotq;
+#pragma unroll
+      for (int m = 0; m < NQ; m++) {
+        S[4 * m] = de * S[4 * m] + kk[m].x * u; S[4 * m + 1] = de * S[4 * m + 1] + kk[m].y * u;
+        S[4 * m + 2] = de * S[4 * m + 2] + kk[m].z * u; S[4 * m + 3] = de * S[4 * m + 3] + kk[m].w * u;
+      }
+      if (live && r == 0) *dst_o = oj;
+      dst_o += o_step;
     }
+  }
+#pragma unroll
+  for (int i = 0; i < DKR; i++) {
+    int d = 4 * DR_LPC * (i >> 2) + 4 * r + (i & 3);
+    if (d < dk) stage[d * 9 + col] = S[i];
+  }
+  asm volatile("bar.sync 1, %0;" ::"n"(DR_THREADS) : "memory");      // the computing threads only: the copying warp has left
+  for (int i = tid; i < dk * 8; i += DR_THREADS) {
+    int d = i >> 3, c = i & 7;
+    if (j0 + c < dv) Sblock[(size_t)d * dv + c] = stage[d * 9 + c];
   }
 }
 

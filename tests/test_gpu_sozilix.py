@@ -353,7 +353,7 @@ class _Ctx:
         self.seq_start = torch.from_numpy(start).to(dev)
         self.tok_seq = torch.from_numpy(np.repeat(np.arange(len(lens), dtype=np.int32), lens)).to(dev)
         self.slots = torch.tensor(slots, dtype=torch.int32, device=dev)
-        self.n_seqs = len(lens)
+        self.n_seqs, self.max_new = len(lens), max(lens)
 
 
 @pytest.mark.parametrize("taps", [1, 2, 4, 7])
@@ -455,4 +455,28 @@ def test_greedy_generation_through_the_entry_point(tmp_path, cfg, seed):
         for i, t in enumerate(g):
             lg = plain.forward(list(p) + g[:i], W, cfg)[-1]
             assert float(lg.max() - lg[t]) <= TOL_BF16 * float(lg.abs().max())
+    llm.unload()
+
+
+def test_random_weights_mode_and_the_command_line(tmp_path):
+    """A model that exists only as a configuration and a seed equals the folder random-weights mode writes for
+    it, and the command line generates from either."""
+    import subprocess
+    import sys
+    from pathlib import Path
+    from scriptling_llm_lib_b200 import llm
+    llm.unload()
+    cfg_path = tmp_path / "cfg.json"
+    cfg_path.write_text(json.dumps(CFG_C))
+    folder = llm.random_model(str(cfg_path), 5, tmp_path / "m")
+    prompt = ids(9, CFG_C["vocab"], 3)
+    a = llm.generate(str(folder), prompt, 6, "greedy", stop_ids=[], dtype="float32")
+    b = llm.generate(f"random:{cfg_path}:5", prompt, 6, "greedy", stop_ids=[], dtype="float32")
+    assert a == b and len(a) == 6
+    root = Path(__file__).resolve().parent.parent
+    out = subprocess.run([sys.executable, str(root / "bin" / "sllm-b200"), "-model", str(tmp_path / "m2"), "-random", str(cfg_path),
+                          "-seed-weights", "5", "-prompt", ",".join(map(str, prompt)), "-tokens", "6", "-dtype", "float32", "-stop", ""],
+                         capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0, out.stderr
+    assert [int(t) for t in out.stdout.replace(",", " ").split()] == a
     llm.unload()
