@@ -21,7 +21,7 @@ class WindowAttentionConfig:
     kv_heads: int
     dim: int                 # width of a query/key head
     vdim: int                # width of a value head
-    window: int              # a position sees itself and the window - 1 before it
+    window: int              # keys visible to a query: its own position and the window - 1 positions behind it
     rot_dims: int            # leading dims of a head that are rotated, in adjacent pairs
     rot_base: float
     scale: float             # multiplies q . k

@@ -1,7 +1,7 @@
 """A short causal convolution over time, one filter per channel, with its last inputs as state.
 
 y_t[c] = act(sum_j w[c, j] * in_{t - taps + 1 + j}[c] + bias[c]) with in = x (+ an input bias), the
-last column of w on the current token and zeros before the sequence's start. A step sees only its
+column taps - 1 of w multiplies the row itself and rows in front of the sequence count as zero. A step sees only its
 own rows, so the taps - 1 inputs before them are per-sequence state (float32), read by the step's
 first rows and replaced at its end; a new sequence starts from zeros, which is the zero padding.
 With `residual` the input is added to the result (y = in + conv(in)). Not a part of its own: mixers

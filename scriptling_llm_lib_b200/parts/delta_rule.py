@@ -5,10 +5,11 @@ From the mixer's input h (no biases): q = Wq h and k = Wk h with n_kv_heads head
 v = Wv h with n_heads heads of width dv; head i reads q/k head i // (n_heads / n_kv_heads). Each of
 q, k, v passes a short causal convolution per channel and SiLU; q and k then become unit vectors per
 head, x / sqrt(sum x^2 + 1e-6), and q is multiplied by dk^-1/2. beta = sigmoid(Wb h) and
-decay = exp(-exp(A_log) * softplus(Wa h + dt_bias)), one each per head. Per head and token, in
-this order: S = decay * S; u = beta * (v - S^T k); S = S + k u^T; o = S^T q (the read-out sees the
-token's own write). o is divided by its root mean square over dv (eps), multiplied by a weight
-[dv] shared by the heads and by silu(Wg h) (laid out heads x dv), and Wo maps back to the hidden width.
+decay = exp(-exp(A_log) * softplus(Wa h + dt_bias)), one each per head. For every head and row the
+state is first shrunk, S = decay * S; then corrected, u = beta * (v - S^T k), S = S + k u^T; then read,
+o = S^T q, i.e. a row's output already contains what the row wrote. The output per head is
+o / rms(o) (over dv, with eps) times a weight vector [dv] that all heads share, times silu(Wg h) taken
+as [heads, dv]; Wo maps the heads' outputs back to the hidden width.
 
 State per sequence: S in float32 and the last taps - 1 inputs of the three convolutions. The
 projections run in the engine's dtype; everything from the convolutions' outputs to the read-out

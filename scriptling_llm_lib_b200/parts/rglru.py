@@ -4,7 +4,7 @@ Two branches of width W from the mixer's input h: y = gelu_tanh(Wy h + by), and 
 a short causal convolution per channel with a bias and no activation. u is cut into `blocks` equal
 parts; in part b, r = sigmoid(Ra[b] u_b + ra_b[b]) and i = sigmoid(Ri[b] u_b + ri_b[b]) with square
 matrices Ra[b], Ri[b] (block-diagonal gates). Per channel: log a = -8 r softplus(lam), a = exp(log a),
-S_t = a S_{t-1} + sqrt(1 - a^2) * i * u, from S = 0, the first token like every other. The mixer's
+S_t = a S_{t-1} + sqrt(1 - a^2) * i * u, starting from S = 0 with the same formula for row 0 as for any row. The mixer's
 output is Wo (S * y).
 
 State per sequence: S [W] in float32 and the convolution's last taps - 1 inputs. Projections run in
