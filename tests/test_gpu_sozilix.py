@@ -50,6 +50,9 @@ CFG_B = config([parallel(attention(2, 2, 64, 64, 70, 64, 10000.0, 0.125), delta(
                width=96, vocab=130, taps=2, mult=1.0, eps=1e-5)
 CFG_C = config([parallel(attention(3, 1, 24, 40, 9, 6, 50.0, 0.2), delta(4, 2, 20, 12, 1), 1.0, 1.0), rglru(40, 2, 1, ff=56)],
                width=72, vocab=77, taps=1, mult=0.3)
+# keys and values both 128 wide (the other width of the tensor-core attention kernels), a delta rule with wide keys
+CFG_D = config([rglru(56, 7, 2), parallel(attention(4, 1, 128, 128, 90, 32, 1000.0, 0.09), delta(2, 2, 160, 24, 3), 0.9, 0.8, ff=64)],
+               width=80, vocab=101, taps=5, mult=0.7, eps=1e-5)
 
 
 def random_weights(cfg, seed, std=0.25):
@@ -171,7 +174,7 @@ def test_the_residual_stream_after_every_layer(tmp_path):
 
 
 # ------------------------------------------------------------------ whole models
-@pytest.mark.parametrize("cfg,seed", [(CFG_A, 1), (CFG_B, 2), (CFG_C, 3)])
+@pytest.mark.parametrize("cfg,seed", [(CFG_A, 1), (CFG_B, 2), (CFG_C, 3), (CFG_D, 4)])
 def test_prompt_portions_and_decoding_agree_with_the_plain_model(tmp_path, cfg, seed):
     W = random_weights(cfg, seed)
     d = write_folder(tmp_path / "m", cfg, W)
