@@ -229,6 +229,14 @@ class KernelSet:
         return self._seq
 
     @property
+    def mix(self) -> "MixKernels":
+        """The kernels of latent attention, decayed linear attention, the selective scan, routed experts and
+        the norm without statistics, for this set's element type."""
+        if getattr(self, "_mix", None) is None:
+            self._mix = MixKernels(self.dtype)
+        return self._mix
+
+    @property
     def decode(self) -> "DecodeKernels":
         if self.dtype != torch.bfloat16:
             raise KernelError("the decode kernels are bfloat16 only")
@@ -699,6 +707,144 @@ class SequenceKernels:
                                       _ptr(ctx.slots, torch.int32, "slots"), _ptr(out, self.dtype, "out"),
                                       _ptr(scratch, torch.float32, "scratch"), c_int(max(1, ctx.max_new)), c_int(T),
                                       c_int(ctx.n_seqs), c_int(W), c_int(block_size), _stream()), "rglru_scan")
+
+
+class MixKernels:
+    """Launchers of mix_kernels.cuh: the norm without statistics fused with the residual sum, activations in
+    place, linear attention with a decay per head, the gated read-out norm over a row, attention over a cached
+    latent (store, absorb, scores and sums, expand), the selective scan, and routed experts (router, pairs one
+    by one, pairs grouped by expert). `dtype` is the element type of activations and weights; state, sums,
+    scores and gates are float32 in both sets."""
+    ACTS = {"gelu_tanh": 1, "relu_squared": 2, "silu": 3}
+    GATES = {"sigmoid": 1, "silu": 2}
+
+    def __init__(self, dtype: torch.dtype):
+        if dtype not in _SUFFIX:
+            raise KernelError(f"no kernels for {dtype}; supported: float32, bfloat16")
+        self.dtype, self.suffix = dtype, _SUFFIX[dtype]
+        self.lib = load_library("mix_" + self.suffix)
+        self._fns: dict[str, object] = {}
+
+    _fn = SequenceKernels._fn
+    _flag = SequenceKernels._flag
+    _view = staticmethod(SequenceKernels._view)
+
+    def dyt_add_norm(self, x, addend, post, rows, weight, bias, alpha, out):
+        """v = x[row] + a, a = the addend ([T, d] of the element type or float32, or float32 [P, T, d] partial
+        sums; None: nothing) passed through tanh(pa * a) * pw + pb when `post` = (pw, pb, pa) is given; x is
+        updated in place when rows is None. out[r] = tanh(alpha * v) * weight + bias. weight, bias, pw, pb float32."""
+        T, d = x.shape
+        n_parts, stride, y_f32 = 0, 0, 0
+        if addend is not None:
+            if tuple(addend.shape[-2:]) != (T, d) or (addend.dim() == 3 and addend.dtype != torch.float32):
+                raise KernelError(f"addend {tuple(addend.shape)} {addend.dtype} does not fit the stream {tuple(x.shape)}")
+            n_parts, stride = (addend.shape[0], T * d) if addend.dim() == 3 else (1, 0)
+            y_f32 = self._flag(addend, "addend")
+        pw, pb, pa = post if post is not None else (None, None, 0.0)
+        _check(self._fn("dyt_add_norm")(
+            _ptr(x, torch.float32, "x"), _ptr(addend, None, "addend"), c_int(y_f32), c_int(n_parts), c_longlong(stride),
+            _ptr(pw, torch.float32, "post weight"), _ptr(pb, torch.float32, "post bias"), c_float(pa),
+            c_int(1 if post is not None else 0), c_int(1), _ptr(rows, torch.int32, "rows"), _ptr(weight, torch.float32, "weight"),
+            _ptr(bias, torch.float32, "bias"), c_float(alpha), c_int(1), _ptr(out, None, "out"), c_int(self._flag(out, "out")),
+            c_int(out.shape[0]), c_int(d), _stream()), "dyt_add_norm")
+
+    def act_inplace(self, x, kind: str):
+        _check(self._fn("act_inplace")(_ptr(x, self.dtype, "x"), c_longlong(x.numel()), c_int(self.ACTS[kind]), _stream()),
+               "act_inplace")
+
+    def lin_attn_decay(self, proj, q_col, k_col, v_col, decay, state, ctx, o, n_heads, dk, dv):
+        """proj [T, ld] of the element type holding the raw q, k, v projections at the given columns (SiLU is
+        applied on reading); decay float32 [H]; state float32 [slots, H, dk, dv] (read and advanced); o float32 [T, H dv]."""
+        if tuple(state.shape[1:]) != (n_heads, dk, dv) or tuple(o.shape) != (proj.shape[0], n_heads * dv):
+            raise KernelError(f"lin_attn_decay shapes: state {tuple(state.shape)}, o {tuple(o.shape)}")
+        _check(self._fn("lin_attn_decay")(
+            _ptr(proj, self.dtype, "proj"), c_int(proj.shape[1]), c_int(q_col), c_int(k_col), c_int(v_col),
+            _ptr(decay, torch.float32, "decay"), _ptr(state, torch.float32, "state"), _ptr(ctx.seq_start, torch.int32, "seq_start"),
+            _ptr(ctx.slots, torch.int32, "slots"), _ptr(o, torch.float32, "o"), c_int(ctx.n_seqs), c_int(max(1, ctx.max_new)),
+            c_int(n_heads), c_int(dk), c_int(dv), c_int(ctx.engine.sm_count), _stream()), "lin_attn_decay")
+
+    def gated_row_rms(self, o, gate, weight, y, eps, gate_act: str):
+        _check(self._fn("gated_row_rms")(_ptr(o, torch.float32, "o"), self._view(gate, "gate"), c_int(gate.stride(0)),
+                                         _ptr(weight, torch.float32, "weight"), c_int(1), _ptr(y, self.dtype, "y"),
+                                         c_int(o.shape[0]), c_int(o.shape[1]), c_float(eps), c_int(self.GATES[gate_act]), _stream()),
+               "gated_row_rms")
+
+    def latent_store(self, q, n_heads, dim, dkv, norm_w, eps, cos_sin, rot, ctx, block_table, pages, rank, rot_dim):
+        """Rotates the last rot_dim dims of every query head of q [T, H (dim + rot_dim)] in place and, with
+        `pages`, stores [dkv[:rank] / rms * norm_w | rotated dkv[rank:]] at the rows' places. q and dkv may be
+        column slices of one buffer."""
+        _check(self._fn("latent_store")(
+            self._view(q, "q"), c_int(q.stride(0)), c_int(n_heads), c_int(dim),
+            self._view(dkv, "dkv") if dkv is not None else c_void_p(0), c_int(dkv.stride(0) if dkv is not None else 0),
+            _ptr(norm_w, torch.float32, "norm weight"), c_int(1), c_float(eps),
+            _ptr(cos_sin, torch.float32, "cos_sin"), c_int(rot), _ptr(ctx.tok_pos, torch.int32, "tok_pos"),
+            _ptr(ctx.tok_seq, torch.int32, "tok_seq"), _ptr(block_table, torch.int32, "block_table"), c_int(block_table.shape[1]),
+            _ptr(pages, self.dtype if pages is not None else None, "pages"), c_int(q.shape[0]), c_int(rank), c_int(rot_dim),
+            _stream()), "latent_store")
+
+    def latent_absorb(self, q, wuk, qa, n_heads, dim, rot_dim, rank, scale):
+        """qa float32 [T, H, rank + rot_dim] = scale * [Wuk_h^T q_h[:dim] | q_h[dim:]] for every head."""
+        if q.dtype != self.dtype:
+            raise KernelError(f"latent_absorb: q has dtype {q.dtype}, expected {self.dtype}")
+        _check(self._fn("latent_absorb")(self._view(q, "q"), c_int(q.stride(0)), _ptr(wuk, self.dtype, "wuk"),
+                                         _ptr(qa, torch.float32, "qa"), c_int(q.shape[0]), c_int(n_heads), c_int(dim),
+                                         c_int(rot_dim), c_int(rank), c_float(scale), _stream()), "latent_absorb")
+
+    def latent_attn(self, qa, pages, ctx, block_table, part, n_heads, rank, rot_dim, n_split):
+        _check(self._fn("latent_attn")(
+            _ptr(qa, torch.float32, "qa"), _ptr(pages, self.dtype, "pages"), _ptr(ctx.tok_pos, torch.int32, "tok_pos"),
+            _ptr(ctx.tok_seq, torch.int32, "tok_seq"), _ptr(block_table, torch.int32, "block_table"), c_int(block_table.shape[1]),
+            _ptr(part, torch.float32, "part"), c_int(qa.shape[0]), c_int(n_heads), c_int(rank), c_int(rot_dim), c_int(n_split),
+            _stream()), "latent_attn")
+
+    def latent_expand(self, part, wuv, out, n_heads, v_dim, rank, n_split):
+        _check(self._fn("latent_expand")(_ptr(part, torch.float32, "part"), _ptr(wuv, self.dtype, "wuv"), _ptr(out, self.dtype, "out"),
+                                         c_int(out.shape[1]), c_int(out.shape[0]), c_int(n_heads), c_int(v_dim), c_int(rank),
+                                         c_int(n_split), _stream()), "latent_expand")
+
+    def selective_scan(self, x, dt_raw, dt_bias, a_log, dskip, bc, b_col, c_col, z, state, ctx, out, inner, n_state):
+        """x, z [T, I] views and bc [T, ...] of the element type (B at b_col, C at c_col), dt_raw float32 [T, I],
+        dt_bias, a_log [I, N], dskip float32; state float32 [slots, I, N] (read and advanced); out [T, I]."""
+        if tuple(state.shape[1:]) != (inner, n_state) or dt_raw.dtype != torch.float32:
+            raise KernelError(f"selective_scan shapes: state {tuple(state.shape)}, dt {dt_raw.dtype}")
+        for t, name in ((x, "x"), (z, "z"), (bc, "bc"), (out, "out")):
+            if t.dtype != self.dtype:
+                raise KernelError(f"selective_scan: {name} has dtype {t.dtype}, expected {self.dtype}")
+        _check(self._fn("selective_scan")(
+            self._view(x, "x"), c_int(x.stride(0)), _ptr(dt_raw, torch.float32, "dt_raw"), c_int(dt_raw.shape[1]),
+            _ptr(dt_bias, torch.float32, "dt_bias"), _ptr(a_log, torch.float32, "a_log"), _ptr(dskip, torch.float32, "dskip"),
+            c_int(1), self._view(bc, "bc"), c_int(bc.stride(0)), c_int(b_col), c_int(c_col), self._view(z, "z"),
+            c_int(z.stride(0)), _ptr(state, torch.float32, "state"), _ptr(ctx.seq_start, torch.int32, "seq_start"),
+            _ptr(ctx.slots, torch.int32, "slots"), self._view(out, "out"), c_int(out.stride(0)), c_int(ctx.n_seqs), c_int(inner),
+            c_int(n_state), _stream()), "selective_scan")
+
+    def moe_route(self, h, wr, correction, idx, wgt, n_groups, keep, top, scale):
+        T, K = h.shape
+        _check(self._fn("moe_route")(self._view(h, "h"), c_int(h.stride(0)), _ptr(wr, self.dtype, "router"),
+                                     _ptr(correction, torch.float32, "correction"), c_int(1), _ptr(idx, torch.int32, "idx"),
+                                     _ptr(wgt, torch.float32, "wgt"), c_int(T), c_int(K), c_int(wr.shape[0]), c_int(n_groups),
+                                     c_int(keep), c_int(top), c_float(scale), _stream()), "moe_route")
+
+    def moe_pairs(self, h, wup, wdown, idx, wgt, hid, out):
+        """wup [E, F, K], wdown [E, N, F]; out float32 [top, T, N] partial sums over a token's chosen experts."""
+        T, K = h.shape
+        top = idx.shape[1]
+        _check(self._fn("moe_pairs")(self._view(h, "h"), c_int(h.stride(0)), _ptr(wup, self.dtype, "wup"),
+                                     _ptr(wdown, self.dtype, "wdown"), _ptr(idx, torch.int32, "idx"), _ptr(wgt, torch.float32, "wgt"),
+                                     _ptr(hid, self.dtype, "hid"), _ptr(out, torch.float32, "out"), c_int(T), c_int(top), c_int(K),
+                                     c_int(wup.shape[1]), c_int(wdown.shape[1]), _stream()), "moe_pairs")
+
+    def moe_grouped(self, h, wup, wdown, idx, wgt, counts, offsets, pair_of_row, hid, out):
+        """The same over pairs grouped by expert (a prompt step). counts int32 [E] must be zero and is left zero."""
+        T, K = h.shape
+        top = idx.shape[1]
+        _check(self._fn("moe_grouped")(self._view(h, "h"), c_int(h.stride(0)), _ptr(wup, self.dtype, "wup"),
+                                       _ptr(wdown, self.dtype, "wdown"), _ptr(idx, torch.int32, "idx"),
+                                       _ptr(wgt, torch.float32, "wgt"), _ptr(counts, torch.int32, "counts"),
+                                       _ptr(offsets, torch.int32, "offsets"), _ptr(pair_of_row, torch.int32, "pair_of_row"),
+                                       _ptr(hid, self.dtype, "hid"), _ptr(out, torch.float32, "out"), c_int(T), c_int(top),
+                                       c_int(wup.shape[0]), c_int(K), c_int(wup.shape[1]), c_int(wdown.shape[1]), _stream()),
+               "moe_grouped")
 
 
 class CastKernels:

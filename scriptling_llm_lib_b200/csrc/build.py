@@ -36,6 +36,8 @@ LIBRARIES: dict[str, tuple[str, tuple[str, ...]]] = {
     "attn_prefill_tcgen05": ("attn_prefill_tcgen05.cu", ("common.cuh", "tcgen05.cuh")),
     "seq_f32": ("lib_seq_f32.cu", ("common.cuh", "sequence_kernels.cuh", "sequence_launchers.inc")),
     "seq_bf16": ("lib_seq_bf16.cu", ("common.cuh", "sequence_kernels.cuh", "sequence_launchers.inc")),
+    "mix_f32": ("lib_mix_f32.cu", ("common.cuh", "mix_kernels.cuh", "mix_launchers.inc")),
+    "mix_bf16": ("lib_mix_bf16.cu", ("common.cuh", "mix_kernels.cuh", "mix_launchers.inc")),
 }
 
 _loaded: dict[str, ctypes.CDLL] = {}

@@ -1,0 +1,767 @@
+// Kernels of further mixers and feed-forwards, and of the norm that stands around them:
+//   - a norm without statistics (tanh(alpha v) w + b), fused with the residual sum in front of it and with the same
+//     kind of norm applied to the addend before it joins the stream;
+//   - elementwise activations of a feed-forward's hidden rows;
+//   - linear attention with a fixed decay per head (a matrix state per head), worked in pieces of rows;
+//   - a read-out norm over the whole row with a gate;
+//   - attention over a cached latent: one vector per position that all heads share (store, query absorption,
+//     scores and sums over the latent, expansion to value heads);
+//   - the selective scan (a state vector per channel whose decay, input and read-out depend on the token);
+//   - routed experts: the router, grouping of (token, expert) pairs by expert, and the experts' products.
+//
+// All of them work on the packed rows of a step (seq_start[b] .. seq_start[b + 1] are the rows of sequence b, in
+// order of position) and find a sequence's state through slots[b]. State, sums, scores, norms, gates and decays are
+// float32 whatever the element type A of activations and weights.
+#pragma once
+#include "common.cuh"
+
+namespace mix {
+
+__device__ __forceinline__ float sigmoid_f(float z) { return 1.0f / (1.0f + expf(-z)); }
+__device__ __forceinline__ float silu_f(float z) { return z / (1.0f + expf(-z)); }
+__device__ __forceinline__ float softplus_f(float z) { return z > 20.0f ? z : log1pf(expf(z)); }
+__device__ __forceinline__ float gelu_tanh_f(float z) {
+  return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
+template <typename A> __device__ __forceinline__ float ld_flag(const void* p, int is_f32, size_t i) {
+  return is_f32 ? ((const float*)p)[i] : to_f32(((const A*)p)[i]);
+}
+template <typename A> __device__ __forceinline__ void st_flag(void* p, int is_f32, size_t i, float v) {
+  if (is_f32) ((float*)p)[i] = v;
+  else ((A*)p)[i] = from_f32<A>(v);
+}
+
+// ------------------------------------------------------------------ residual sum + norm without statistics
+// a = sum of the addend's parts (one [T, d] tensor of the element type or float32, or P float32 partial sums);
+// with a norm of its own: a <- tanh(pa * a) * pw + pb. v = x[row] + a (x updated in place when rows == nullptr and
+// there is an addend). out[r] = tanh(alpha * v) * w + b. Every element on its own: no sums over the row.
+struct DytArgs {
+  float* x;
+  const void* y; int y_f32; int n_parts; long long part_stride;
+  const void* pw; const void* pb; float palpha; int has_post; int p_f32;
+  const int* rows;
+  const void* w; const void* b; float alpha; int w_f32;
+  void* out; int out_f32;
+  int d;
+};
+
+template <typename A>
+__global__ void dyt_add_norm_kernel(DytArgs p) {
+  int r = blockIdx.x;
+  size_t in = p.rows ? (size_t)p.rows[r] : (size_t)r;
+  bool update = p.rows == nullptr && p.y != nullptr;
+  for (int j = blockIdx.y * blockDim.x + threadIdx.x; j < p.d; j += gridDim.y * blockDim.x) {
+    float v = p.x[in * p.d + j];
+    if (p.y) {
+      float a = 0.f;
+      for (int k = 0; k < p.n_parts; k++) a += ld_flag<A>(p.y, p.y_f32, (size_t)k * p.part_stride + in * p.d + j);
+      if (p.has_post) a = tanhf(p.palpha * a) * load_w(p.pw, p.p_f32, j) + load_w(p.pb, p.p_f32, j);
+      v += a;
+      if (update) p.x[in * p.d + j] = v;
+    }
+    if (p.out) st_flag<A>(p.out, p.out_f32, (size_t)r * p.d + j, tanhf(p.alpha * v) * load_w(p.w, p.w_f32, j) + load_w(p.b, p.w_f32, j));
+  }
+}
+
+// ------------------------------------------------------------------ activations in place
+// kind 1: the tanh form of gelu; 2: the square of relu; 3: silu
+template <typename A>
+__global__ void act_inplace_kernel(A* __restrict__ x, long long n, int kind) {
+  long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  float z = to_f32(x[i]);
+  float y = kind == 1 ? gelu_tanh_f(z) : kind == 2 ? (z > 0.f ? z * z : 0.f) : silu_f(z);
+  x[i] = from_f32<A>(y);
+}
+
+// ------------------------------------------------------------------ linear attention with a decay per head
+// Per head: S_t = decay * S_{t-1} + k_t v_t^T, o_t = S_t^T q_t, with q, k, v = silu of the projected rows (columns
+// q_col, k_col, v_col of `proj`, heads side by side). A block owns VT value columns of one head of one sequence and
+// walks the sequence's rows in pieces of at most C rows. Within a piece of n rows (decay^m written g^m):
+//   P[i][j] = g^(i-j) q_i . k_j (j <= i);  o_i = g^(i+1) S^T q_i + sum_j P[i][j] v_j;
+//   S <- g^n S + sum_j g^(n-1-j) k_j v_j^T.
+// All in float32 out of shared memory, 4 x 4 outputs a thread. The state [slot][head][D][V] is read at the start
+// and written at the end.
+template <typename A>
+__global__ void __launch_bounds__(256) lin_attn_decay_kernel(const A* __restrict__ proj, int ld, int q_col, int k_col, int v_col,
+                                                             const float* __restrict__ decay, float* __restrict__ state,
+                                                             const int* __restrict__ seq_start, const int* __restrict__ slots,
+                                                             float* __restrict__ o, int H, int D, int V, int VT, int C) {
+  extern __shared__ __align__(16) float sm[];
+  int b = blockIdx.z, h = blockIdx.y, c0 = blockIdx.x * VT;
+  int vt = min(VT, V - c0);
+  int Dp = (D + 3) & ~3, VTp = (VT + 3) & ~3;
+  int qs_ld = Dp + 4;
+  float* S = sm;                                  // [Dp][VTp]
+  float* qs = S + (size_t)Dp * VTp;               // [C][qs_ld]
+  float* ks = qs + (size_t)C * qs_ld;             // [C][qs_ld]
+  float* vs = ks + (size_t)C * qs_ld;             // [C][VTp]
+  float* P = vs + (size_t)C * VTp;                // [C][C]
+  float* pw = P + (size_t)C * C;                  // [C + 2] powers of the decay
+  int tid = threadIdx.x;
+  float g = decay[h];
+  if (tid == 0) {
+    float a = 1.f;
+    for (int i = 0; i <= C + 1; i++) { pw[i] = a; a *= g; }
+  }
+  float* st = state + ((size_t)slots[b] * H + h) * D * V;
+  for (int i = tid; i < Dp * VTp; i += 256) {
+    int d = i / VTp, c = i % VTp;
+    S[i] = (d < D && c < vt) ? st[(size_t)d * V + c0 + c] : 0.f;
+  }
+  int r_begin = seq_start[b], r_end = seq_start[b + 1];
+  for (int r0 = r_begin; r0 < r_end; r0 += C) {
+    int n = min(C, r_end - r0);
+    __syncthreads();
+    for (int i = tid; i < C * Dp; i += 256) {
+      int r = i / Dp, d = i % Dp;
+      float qv = 0.f, kv = 0.f;
+      if (r < n && d < D) {
+        const A* row = proj + (size_t)(r0 + r) * ld + (size_t)h * D + d;
+        qv = silu_f(to_f32(row[q_col]));
+        kv = silu_f(to_f32(row[k_col]));
+      }
+      qs[r * qs_ld + d] = qv;
+      ks[r * qs_ld + d] = kv;
+    }
+    for (int i = tid; i < C * VTp; i += 256) {
+      int r = i / VTp, c = i % VTp;
+      float vv = 0.f;
+      if (r < n && c < vt) vv = silu_f(to_f32(proj[(size_t)(r0 + r) * ld + v_col + (size_t)h * V + c0 + c]));
+      vs[i] = vv;
+    }
+    __syncthreads();
+    // scores inside the piece
+    for (int i = tid; i < C * C; i += 256) {
+      int qi = i / C, kj = i % C;
+      float s = 0.f;
+      if (kj <= qi && qi < n) {
+        const float4* a = (const float4*)(qs + qi * qs_ld);
+        const float4* bb = (const float4*)(ks + kj * qs_ld);
+        float s0 = 0.f, s1 = 0.f;
+        for (int d = 0; d < Dp / 4; d++) {
+          float4 x = a[d], y = bb[d];
+          s0 += x.x * y.x + x.z * y.z;
+          s1 += x.y * y.y + x.w * y.w;
+        }
+        s = (s0 + s1) * pw[qi - kj];
+      }
+      P[i] = s;
+    }
+    __syncthreads();
+    // outputs of the piece: 4 rows x 4 columns a thread
+    int n4 = (n + 3) / 4, c4 = VTp / 4;
+    for (int it = tid; it < n4 * c4; it += 256) {
+      int i0 = (it / c4) * 4, cc = (it % c4) * 4;
+      float acc[4][4];
+#pragma unroll
+      for (int a = 0; a < 4; a++)
+#pragma unroll
+        for (int c = 0; c < 4; c++) acc[a][c] = 0.f;
+      for (int d = 0; d < D; d++) {
+        float4 sv = *(const float4*)(S + (size_t)d * VTp + cc);
+#pragma unroll
+        for (int a = 0; a < 4; a++) {
+          float qv = (i0 + a < C) ? qs[(i0 + a) * qs_ld + d] : 0.f;
+          acc[a][0] += qv * sv.x; acc[a][1] += qv * sv.y; acc[a][2] += qv * sv.z; acc[a][3] += qv * sv.w;
+        }
+      }
+#pragma unroll
+      for (int a = 0; a < 4; a++) {
+        float f = pw[min(i0 + a + 1, C + 1)];
+#pragma unroll
+        for (int c = 0; c < 4; c++) acc[a][c] *= f;
+      }
+      int jmax = min(i0 + 3, n - 1);
+      for (int j = 0; j <= jmax; j++) {
+        float4 vv = *(const float4*)(vs + (size_t)j * VTp + cc);
+#pragma unroll
+        for (int a = 0; a < 4; a++) {
+          float pv = (i0 + a < C) ? P[(i0 + a) * C + j] : 0.f;      // zero above the diagonal
+          acc[a][0] += pv * vv.x; acc[a][1] += pv * vv.y; acc[a][2] += pv * vv.z; acc[a][3] += pv * vv.w;
+        }
+      }
+#pragma unroll
+      for (int a = 0; a < 4; a++) {
+        if (i0 + a >= n) continue;
+        float* orow = o + (size_t)(r0 + i0 + a) * H * V + (size_t)h * V + c0 + cc;
+#pragma unroll
+        for (int c = 0; c < 4; c++)
+          if (cc + c < vt) orow[c] = acc[a][c];
+      }
+    }
+    __syncthreads();
+    // the state after the piece: 4 key dims x 4 columns a thread
+    float gn = pw[n];
+    int d4 = Dp / 4;
+    for (int it = tid; it < d4 * c4; it += 256) {
+      int d0 = (it / c4) * 4, cc = (it % c4) * 4;
+      float acc[4][4];
+#pragma unroll
+      for (int a = 0; a < 4; a++) {
+        float4 sv = *(const float4*)(S + (size_t)(d0 + a) * VTp + cc);
+        acc[a][0] = gn * sv.x; acc[a][1] = gn * sv.y; acc[a][2] = gn * sv.z; acc[a][3] = gn * sv.w;
+      }
+      for (int j = 0; j < n; j++) {
+        float f = pw[n - 1 - j];
+        float4 kv = *(const float4*)(ks + (size_t)j * qs_ld + d0);
+        float4 vv = *(const float4*)(vs + (size_t)j * VTp + cc);
+        vv.x *= f; vv.y *= f; vv.z *= f; vv.w *= f;
+        acc[0][0] += kv.x * vv.x; acc[0][1] += kv.x * vv.y; acc[0][2] += kv.x * vv.z; acc[0][3] += kv.x * vv.w;
+        acc[1][0] += kv.y * vv.x; acc[1][1] += kv.y * vv.y; acc[1][2] += kv.y * vv.z; acc[1][3] += kv.y * vv.w;
+        acc[2][0] += kv.z * vv.x; acc[2][1] += kv.z * vv.y; acc[2][2] += kv.z * vv.z; acc[2][3] += kv.z * vv.w;
+        acc[3][0] += kv.w * vv.x; acc[3][1] += kv.w * vv.y; acc[3][2] += kv.w * vv.z; acc[3][3] += kv.w * vv.w;
+      }
+#pragma unroll
+      for (int a = 0; a < 4; a++)
+        *(float4*)(S + (size_t)(d0 + a) * VTp + cc) = make_float4(acc[a][0], acc[a][1], acc[a][2], acc[a][3]);
+    }
+  }
+  __syncthreads();
+  for (int i = tid; i < Dp * VTp; i += 256) {
+    int d = i / VTp, c = i % VTp;
+    if (d < D && c < vt) st[(size_t)d * V + c0 + c] = S[i];
+  }
+}
+
+// ------------------------------------------------------------------ read-out norm over the whole row with a gate
+// y[t] = o[t] / sqrt(mean(o[t]^2) + eps) * w * gate(g[t]); gate_act 1: sigmoid, 2: silu. o float32 [T, W]; g a column
+// slice of the projections (element type).
+template <typename A>
+__global__ void gated_row_rms_kernel(const float* __restrict__ o, const A* __restrict__ g, int ldg, const void* __restrict__ w,
+                                     int w_f32, A* __restrict__ y, int W, float eps, int gate_act) {
+  __shared__ float red[32];
+  int t = blockIdx.x;
+  const float* orow = o + (size_t)t * W;
+  float ss = 0.f;
+  for (int j = threadIdx.x; j < W; j += blockDim.x) ss += orow[j] * orow[j];
+  ss = block_sum(ss, red);
+  float inv = 1.0f / sqrtf(ss / (float)W + eps);
+  for (int j = threadIdx.x; j < W; j += blockDim.x) {
+    float z = to_f32(g[(size_t)t * ldg + j]);
+    float gate = gate_act == 1 ? sigmoid_f(z) : silu_f(z);
+    y[(size_t)t * W + j] = from_f32<A>(orow[j] * inv * load_w(w, w_f32, j) * gate);
+  }
+}
+
+// ------------------------------------------------------------------ attention over a cached latent
+// A position keeps one vector [R + P]: the latent c (the first R of the down-projection's output divided by their
+// root mean square, times a weight) and a key part of P dims rotated by its position, shared by all heads. Pages:
+// [page][SLLM_PAGE][R + P] of the element type.
+//
+// store: one block per row. Writes [c | rotated key part] at the row's place (when pages != nullptr) and rotates
+// the last P dims of every query head in place (the leading `rot` of them, in adjacent pairs, by the table
+// [position][rot / 2] of (cos, sin)).
+template <typename A>
+__global__ void latent_store_kernel(A* __restrict__ q, int ldq, int H, int D, const A* __restrict__ dkv, int ldk,
+                                    const void* __restrict__ nw, int nw_f32, float eps, const float2* __restrict__ cos_sin,
+                                    int rot, const int* __restrict__ tok_pos, const int* __restrict__ tok_seq,
+                                    const int* __restrict__ block_table, int max_pages, A* __restrict__ pages, int R, int P) {
+  __shared__ float red[32];
+  int t = blockIdx.x;
+  int pos = tok_pos[t];
+  const float2* cs = cos_sin + (size_t)pos * (rot / 2);
+  for (int i = threadIdx.x; i < H * (rot / 2); i += blockDim.x) {
+    int h = i / (rot / 2), pr = i % (rot / 2);
+    A* qp = q + (size_t)t * ldq + (size_t)h * (D + P) + D + 2 * pr;
+    float u = to_f32(qp[0]), v = to_f32(qp[1]);
+    float2 c = cs[pr];
+    qp[0] = from_f32<A>(u * c.x - v * c.y);
+    qp[1] = from_f32<A>(v * c.x + u * c.y);
+  }
+  if (!pages) return;
+  const A* row = dkv + (size_t)t * ldk;
+  float ss = 0.f;
+  for (int j = threadIdx.x; j < R; j += blockDim.x) {
+    float v = to_f32(row[j]);
+    ss += v * v;
+  }
+  ss = block_sum(ss, red);
+  float inv = 1.0f / sqrtf(ss / (float)R + eps);
+  int page = block_table[(size_t)tok_seq[t] * max_pages + pos / SLLM_PAGE];
+  A* dst = pages + ((size_t)page * SLLM_PAGE + pos % SLLM_PAGE) * (R + P);
+  for (int j = threadIdx.x; j < R; j += blockDim.x) dst[j] = from_f32<A>(to_f32(row[j]) * inv * load_w(nw, nw_f32, j));
+  for (int pr = threadIdx.x; pr < P / 2 + (P & 1); pr += blockDim.x) {
+    if (2 * pr + 1 < P && pr < rot / 2) {
+      float u = to_f32(row[R + 2 * pr]), v = to_f32(row[R + 2 * pr + 1]);
+      float2 c = cs[pr];
+      dst[R + 2 * pr] = from_f32<A>(u * c.x - v * c.y);
+      dst[R + 2 * pr + 1] = from_f32<A>(v * c.x + u * c.y);
+    } else {
+      dst[R + 2 * pr] = row[R + 2 * pr];
+      if (2 * pr + 1 < P) dst[R + 2 * pr + 1] = row[R + 2 * pr + 1];
+    }
+  }
+}
+
+// absorb: the query a head asks the latent with. qa[t][h] = scale * [ Wuk_h^T q_unrot | q_rot ] (float32, R + P
+// wide), Wuk_h = rows h D .. h D + D - 1 of the stored [H D, R] matrix. A block takes up to 8 rows of one head;
+// threads run over the latent's columns, so a row of the matrix is read in one piece.
+#define MIX_ABSORB_ROWS 8
+template <typename A>
+__global__ void __launch_bounds__(128) latent_absorb_kernel(const A* __restrict__ q, int ldq, const A* __restrict__ wuk,
+                                                            float* __restrict__ qa, int T, int H, int D, int P, int R,
+                                                            float scale) {
+  extern __shared__ __align__(16) float sm[];     // [8][D]
+  int h = blockIdx.y, t0 = blockIdx.x * MIX_ABSORB_ROWS;
+  int n = min(MIX_ABSORB_ROWS, T - t0);
+  for (int i = threadIdx.x; i < MIX_ABSORB_ROWS * D; i += blockDim.x) {
+    int r = i / D, d = i % D;
+    sm[i] = r < n ? to_f32(q[(size_t)(t0 + r) * ldq + (size_t)h * (D + P) + d]) * scale : 0.f;
+  }
+  __syncthreads();
+  const A* w = wuk + (size_t)h * D * R;
+  for (int c = threadIdx.x; c < R; c += blockDim.x) {
+    float acc[MIX_ABSORB_ROWS];
+#pragma unroll
+    for (int r = 0; r < MIX_ABSORB_ROWS; r++) acc[r] = 0.f;
+    for (int d = 0; d < D; d++) {
+      float wv = to_f32(w[(size_t)d * R + c]);
+#pragma unroll
+      for (int r = 0; r < MIX_ABSORB_ROWS; r++) acc[r] += sm[r * D + d] * wv;
+    }
+    for (int r = 0; r < n; r++) qa[((size_t)(t0 + r) * H + h) * (R + P) + c] = acc[r];
+  }
+  for (int i = threadIdx.x; i < n * P; i += blockDim.x) {
+    int r = i / P, j = i % P;
+    qa[((size_t)(t0 + r) * H + h) * (R + P) + R + j] = to_f32(q[(size_t)(t0 + r) * ldq + (size_t)h * (D + P) + D + j]) * scale;
+  }
+}
+
+// scores and sums: one block per (row, group of up to 8 heads, split of the keys), a warp per head. Keys arrive in
+// tiles of 32 rows, staged in shared memory as floats once for all heads of the block; a lane scores one key of the
+// tile, softmax statistics are renewed once per tile, and the sum over the latent runs with the columns spread over
+// the lanes (NV columns a lane). Causal: keys 0 .. pos of the row's sequence. Each split leaves (max, sum, sums over
+// the latent) in `part` [T][H][n_split][R + 2]; the expansion merges them.
+template <typename A, int NV>
+__global__ void __launch_bounds__(256) latent_attn_kernel(const float* __restrict__ qa, const A* __restrict__ pages,
+                                                          const int* __restrict__ tok_pos, const int* __restrict__ tok_seq,
+                                                          const int* __restrict__ block_table, int max_pages,
+                                                          float* __restrict__ part, int H, int R, int P, int n_split) {
+  extern __shared__ __align__(16) float sm[];
+  int W = R + P, Wp = W + 1;
+  int t = blockIdx.x, h0 = blockIdx.y * 8, sp = blockIdx.z;
+  int nh = min(8, H - h0);
+  int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  int nthreads = blockDim.x;
+  float* qs = sm;                                 // [8][W]
+  float* Ks = qs + 8 * W;                         // [32][Wp]
+  int pos = tok_pos[t];
+  const int* pt = block_table + (size_t)tok_seq[t] * max_pages;
+  for (int i = threadIdx.x; i < nh * W; i += nthreads) qs[i] = qa[((size_t)t * H + h0) * W + i];
+  int n_tiles = pos / 32 + 1;
+  int per = (n_tiles + n_split - 1) / n_split;
+  int tile_lo = sp * per, tile_hi = min(n_tiles, tile_lo + per);
+  float m = -INFINITY, l = 0.f, acc[NV];
+#pragma unroll
+  for (int i = 0; i < NV; i++) acc[i] = 0.f;
+  bool active = wid < nh;
+  const float* myq = qs + wid * W;
+  for (int tile = tile_lo; tile < tile_hi; tile++) {
+    int k0 = tile * 32;
+    int nk = min(32, pos + 1 - k0);
+    __syncthreads();
+    for (int i = threadIdx.x; i < 32 * W; i += nthreads) {
+      int kr = i / W, d = i % W;
+      float v = 0.f;
+      if (kr < nk) {
+        int kp = k0 + kr;
+        v = to_f32(pages[((size_t)pt[kp / SLLM_PAGE] * SLLM_PAGE + kp % SLLM_PAGE) * W + d]);
+      }
+      Ks[kr * Wp + d] = v;
+    }
+    __syncthreads();
+    if (!active) continue;
+    float sc = -INFINITY;
+    if (lane < nk) {
+      const float* kr = Ks + lane * Wp;
+      float s0 = 0.f, s1 = 0.f;
+      int d = 0;
+      for (; d + 1 < W; d += 2) { s0 += myq[d] * kr[d]; s1 += myq[d + 1] * kr[d + 1]; }
+      if (d < W) s0 += myq[d] * kr[d];
+      sc = s0 + s1;
+    }
+    float m_new = fmaxf(m, warp_max(sc));
+    float c = expf(m - m_new);
+    float pwt = lane < nk ? expf(sc - m_new) : 0.f;
+    l = l * c + warp_sum(pwt);
+    m = m_new;
+#pragma unroll
+    for (int i = 0; i < NV; i++) acc[i] *= c;
+    for (int j = 0; j < nk; j++) {
+      float pj = __shfl_sync(0xffffffffu, pwt, j);
+      const float* kr = Ks + j * Wp;
+#pragma unroll
+      for (int i = 0; i < NV; i++) {
+        int col = lane + 32 * i;
+        if (col < R) acc[i] += pj * kr[col];
+      }
+    }
+  }
+  if (!active) return;
+  float* dst = part + (((size_t)t * H + h0 + wid) * n_split + sp) * (R + 2);
+  if (lane == 0) { dst[0] = m; dst[1] = l; }
+#pragma unroll
+  for (int i = 0; i < NV; i++) {
+    int col = lane + 32 * i;
+    if (col < R) dst[2 + col] = acc[i];
+  }
+}
+
+// expand: merges the splits' sums over the latent and maps them to the head's values: out[t][h V + v] =
+// Wuv[h V + v] . (sum_s w_s acc_s / sum_s w_s l_s), w_s = exp(m_s - max m). A block takes up to 8 rows of one head,
+// a warp an output column at a time.
+template <typename A>
+__global__ void __launch_bounds__(128) latent_expand_kernel(const float* __restrict__ part, const A* __restrict__ wuv,
+                                                            A* __restrict__ out, int ldo, int T, int H, int V, int R,
+                                                            int n_split) {
+  extern __shared__ __align__(16) float sm[];     // [8][R]
+  int h = blockIdx.y, t0 = blockIdx.x * MIX_ABSORB_ROWS;
+  int n = min(MIX_ABSORB_ROWS, T - t0);
+  int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  for (int r = 0; r < MIX_ABSORB_ROWS; r++) {
+    if (r >= n) {
+      for (int c = threadIdx.x; c < R; c += blockDim.x) sm[r * R + c] = 0.f;
+      continue;
+    }
+    const float* p0 = part + ((size_t)(t0 + r) * H + h) * n_split * (R + 2);
+    float mx = -INFINITY;
+    for (int s = 0; s < n_split; s++) mx = fmaxf(mx, p0[(size_t)s * (R + 2)]);
+    float den = 0.f;
+    for (int s = 0; s < n_split; s++) {
+      float ms = p0[(size_t)s * (R + 2)];
+      if (ms > -INFINITY) den += expf(ms - mx) * p0[(size_t)s * (R + 2) + 1];
+    }
+    float inv = 1.0f / den;
+    for (int c = threadIdx.x; c < R; c += blockDim.x) {
+      float a = 0.f;
+      for (int s = 0; s < n_split; s++) {
+        float ms = p0[(size_t)s * (R + 2)];
+        if (ms > -INFINITY) a += expf(ms - mx) * p0[(size_t)s * (R + 2) + 2 + c];
+      }
+      sm[r * R + c] = a * inv;
+    }
+  }
+  __syncthreads();
+  for (int v = wid; v < V; v += nw) {
+    const A* w = wuv + ((size_t)h * V + v) * R;
+    float acc[MIX_ABSORB_ROWS];
+#pragma unroll
+    for (int r = 0; r < MIX_ABSORB_ROWS; r++) acc[r] = 0.f;
+    for (int c = lane; c < R; c += 32) {
+      float wv = to_f32(w[c]);
+#pragma unroll
+      for (int r = 0; r < MIX_ABSORB_ROWS; r++) acc[r] += sm[r * R + c] * wv;
+    }
+#pragma unroll
+    for (int r = 0; r < MIX_ABSORB_ROWS; r++) acc[r] = warp_sum(acc[r]);
+    if (lane == 0)
+      for (int r = 0; r < n; r++) out[(size_t)(t0 + r) * ldo + (size_t)h * V + v] = from_f32<A>(acc[r]);
+  }
+}
+
+// ------------------------------------------------------------------ the selective scan
+// Per channel c a state S[c][0..N): for each row dt = softplus(dt_raw[c] + dt_bias[c]);
+// S[c][n] <- exp(dt * A[c][n]) * S[c][n] + dt * x[c] * B[n];  y[c] = sum_n S[c][n] * C[n] + D[c] * x[c];  out = y * silu(z[c]),
+// A = -exp(A_log). Four lanes share a channel (every fourth state each); a block takes 32 channels of one sequence and
+// walks its rows. x, z, B, C: column slices of buffers of the element type; dt_raw float32.
+struct ScanArgs {
+  const void* x; int ldx;
+  const float* dt_raw; int lddt;
+  const void* dt_bias; const void* a_log; const void* dskip; int w_f32;
+  const void* bc; int ldbc; int b_col; int c_col;
+  const void* z; int ldz;
+  float* state;
+  const int* seq_start; const int* slots;
+  void* out; int ldo;
+  int I, N;
+};
+
+template <typename A, int NPL>
+__global__ void __launch_bounds__(128) selective_scan_kernel(ScanArgs p) {
+  int b = blockIdx.y;
+  int ch = blockIdx.x * 32 + (threadIdx.x >> 2), l = threadIdx.x & 3;
+  bool live = ch < p.I;
+  int c = live ? ch : p.I - 1;
+  float Areg[NPL], S[NPL];
+  float* st = p.state + ((size_t)p.slots[b] * p.I + c) * p.N;
+#pragma unroll
+  for (int i = 0; i < NPL; i++) {
+    int n = l + 4 * i;
+    Areg[i] = n < p.N ? -expf(load_w(p.a_log, p.w_f32, (size_t)c * p.N + n)) : 0.f;
+    S[i] = n < p.N ? st[n] : 0.f;
+  }
+  float bias = load_w(p.dt_bias, p.w_f32, c), dsk = load_w(p.dskip, p.w_f32, c);
+  const A* xs = (const A*)p.x;
+  const A* zs = (const A*)p.z;
+  const A* bcs = (const A*)p.bc;
+  A* out = (A*)p.out;
+  int r_end = p.seq_start[b + 1];
+  for (int r = p.seq_start[b]; r < r_end; r++) {
+    float dt = softplus_f(p.dt_raw[(size_t)r * p.lddt + c] + bias);
+    float xv = to_f32(xs[(size_t)r * p.ldx + c]);
+    float dx = dt * xv;
+    const A* brow = bcs + (size_t)r * p.ldbc;
+    float acc = 0.f;
+#pragma unroll
+    for (int i = 0; i < NPL; i++) {
+      int n = l + 4 * i;
+      if (n < p.N) {
+        S[i] = expf(dt * Areg[i]) * S[i] + dx * to_f32(brow[p.b_col + n]);
+        acc += S[i] * to_f32(brow[p.c_col + n]);
+      }
+    }
+    acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+    acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+    if (l == 0 && live) {
+      float y = acc + dsk * xv;
+      out[(size_t)r * p.ldo + c] = from_f32<A>(y * silu_f(to_f32(zs[(size_t)r * p.ldz + c])));
+    }
+  }
+  if (live) {
+#pragma unroll
+    for (int i = 0; i < NPL; i++) {
+      int n = l + 4 * i;
+      if (n < p.N) st[n] = S[i];
+    }
+  }
+}
+
+// ------------------------------------------------------------------ routed experts
+// router: one block per token. z = Wr h (float32 sums), s = sigmoid(z), choice = s + correction. Experts form
+// n_groups equal groups of neighbours; a group's score is the sum of its two largest choices; only experts of the
+// `keep` best groups can be chosen; the `top` largest choices among them are taken (ties: the lower index). Their
+// weights are s / (sum of the chosen s + 1e-20) * scale. idx int32 [T][top], wgt float32 [T][top].
+template <typename A>
+__global__ void __launch_bounds__(128) moe_route_kernel(const A* __restrict__ h, int ldh, const A* __restrict__ wr,
+                                                        const void* __restrict__ corr, int corr_f32, int* __restrict__ idx,
+                                                        float* __restrict__ wgt, int K, int E, int n_groups, int keep, int top,
+                                                        float scale) {
+  extern __shared__ __align__(16) float sm[];
+  float* s = sm;                    // [E] sigmoid scores
+  float* ch = s + E;                // [E] choice scores (minus infinity once taken or shut out)
+  float* gs = ch + E;               // [n_groups]
+  int t = blockIdx.x;
+  int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  const A* x = h + (size_t)t * ldh;
+  for (int e = wid; e < E; e += nw) {
+    const A* w = wr + (size_t)e * K;
+    float a = 0.f;
+    for (int k = lane; k < K; k += 32) a += to_f32(x[k]) * to_f32(w[k]);
+    a = warp_sum(a);
+    if (lane == 0) {
+      float sg = sigmoid_f(a);
+      s[e] = sg;
+      ch[e] = sg + load_w(corr, corr_f32, e);
+    }
+  }
+  __syncthreads();
+  if (wid != 0) return;
+  int gsz = E / n_groups;
+  if (n_groups > 1) {
+    for (int g = lane; g < n_groups; g += 32) {
+      float a = -INFINITY, b2 = -INFINITY;
+      for (int j = 0; j < gsz; j++) {
+        float v = ch[g * gsz + j];
+        if (v > a) { b2 = a; a = v; }
+        else if (v > b2) b2 = v;
+      }
+      gs[g] = gsz > 1 ? a + b2 : a;
+    }
+    __syncwarp();
+    // the groups that are not kept: n_groups - keep rounds of taking the smallest out (ties: the higher index goes)
+    for (int round = 0; round < n_groups - keep; round++) {
+      float best = INFINITY;
+      int bi = -1;
+      for (int g = lane; g < n_groups; g += 32) {
+        float v = gs[g];
+        if (v <= best && v < INFINITY) { best = v; bi = g; }      // later (higher) index wins ties inside a lane
+      }
+      for (int o = 16; o > 0; o >>= 1) {
+        float ob = __shfl_xor_sync(0xffffffffu, best, o);
+        int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (oi >= 0 && (bi < 0 || ob < best || (ob == best && oi > bi))) { best = ob; bi = oi; }
+      }
+      if (bi < 0) break;
+      if (lane == 0) gs[bi] = INFINITY;           // marks a group that is shut out
+      for (int j = lane; j < gsz; j += 32) ch[bi * gsz + j] = -INFINITY;
+      __syncwarp();
+    }
+  }
+  __syncwarp();
+  float sum = 0.f;
+  for (int k = 0; k < top; k++) {
+    float best = -INFINITY;
+    int bi = -1;
+    for (int e = lane; e < E; e += 32) {
+      float v = ch[e];
+      if (v > best) { best = v; bi = e; }         // the lower index wins ties inside a lane
+    }
+    for (int o = 16; o > 0; o >>= 1) {
+      float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (oi >= 0 && (bi < 0 || ob > best || (ob == best && oi < bi))) { best = ob; bi = oi; }
+    }
+    if (bi < 0) bi = 0;                           // fewer experts allowed than asked for: cannot happen with a checked configuration
+    float sv = s[bi];
+    sum += sv;
+    if (lane == 0) {
+      idx[(size_t)t * top + k] = bi;
+      wgt[(size_t)t * top + k] = sv;
+      ch[bi] = -INFINITY;
+    }
+    __syncwarp();
+  }
+  float f = scale / (sum + 1e-20f);
+  for (int k = lane; k < top; k += 32) wgt[(size_t)t * top + k] *= f;
+}
+
+// Few rows (a decode step): every (token, chosen expert) pair on its own, a warp per output column.
+//   up:   hid[p][f] = relu(Wup[e_p][f] . h[t_p])^2           p = t * top + k
+//   down: out[k][t][j] = wgt[p] * (Wdown[e_p][j] . hid[p])    float32 partial sums over k, added by the reader
+template <typename A>
+__global__ void __launch_bounds__(128) moe_pair_up_kernel(const A* __restrict__ h, int ldh, const A* __restrict__ wup,
+                                                          const int* __restrict__ idx, A* __restrict__ hid, int top, int K, int F) {
+  int p = blockIdx.y;
+  int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  int f = blockIdx.x * nw + wid;
+  if (f >= F) return;
+  const A* x = h + (size_t)(p / top) * ldh;
+  const A* w = wup + ((size_t)idx[p] * F + f) * K;
+  float a = 0.f;
+  for (int k = lane; k < K; k += 32) a += to_f32(x[k]) * to_f32(w[k]);
+  a = warp_sum(a);
+  if (lane == 0) hid[(size_t)p * F + f] = from_f32<A>(a > 0.f ? a * a : 0.f);
+}
+
+template <typename A>
+__global__ void __launch_bounds__(128) moe_pair_down_kernel(const A* __restrict__ hid, const A* __restrict__ wdown,
+                                                            const int* __restrict__ idx, const float* __restrict__ wgt,
+                                                            float* __restrict__ out, int T, int top, int F, int N) {
+  int p = blockIdx.y;
+  int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  int j = blockIdx.x * nw + wid;
+  if (j >= N) return;
+  const A* x = hid + (size_t)p * F;
+  const A* w = wdown + ((size_t)idx[p] * N + j) * F;
+  float a = 0.f;
+  for (int k = lane; k < F; k += 32) a += to_f32(x[k]) * to_f32(w[k]);
+  a = warp_sum(a);
+  if (lane == 0) out[((size_t)(p % top) * T + p / top) * N + j] = wgt[p] * a;
+}
+
+// Many rows (a prompt step): the pairs are grouped by expert. count: how many pairs every expert got;
+// offsets: their prefix sums (one block); place: every pair's row in the grouped order (pairs of one expert in
+// any order: a row's result does not depend on its place).
+__global__ void moe_count_kernel(const int* __restrict__ idx, int n_pairs, int* __restrict__ counts) {
+  int p = blockIdx.x * blockDim.x + threadIdx.x;
+  if (p < n_pairs) atomicAdd(&counts[idx[p]], 1);
+}
+__global__ void moe_offsets_kernel(int* __restrict__ counts, int* __restrict__ offsets, int E) {
+  if (threadIdx.x == 0) {
+    int a = 0;
+    for (int e = 0; e < E; e++) {
+      offsets[e] = a;
+      a += counts[e];
+      counts[e] = 0;                              // reused as the fill counters of the placing pass
+    }
+    offsets[E] = a;
+  }
+}
+__global__ void moe_place_kernel(const int* __restrict__ idx, int n_pairs, const int* __restrict__ offsets,
+                                 int* __restrict__ fill, int* __restrict__ pair_of_row) {
+  int p = blockIdx.x * blockDim.x + threadIdx.x;
+  if (p >= n_pairs) return;
+  int e = idx[p];
+  pair_of_row[offsets[e] + atomicAdd(&fill[e], 1)] = p;
+}
+
+// The experts' products over the grouped rows: tiles of 64 rows x 64 columns of one expert, 16 of K at a time
+// through shared memory, 4 x 4 outputs a thread, float32 sums. Tile `blockIdx.x` of the rows: the experts' row
+// ranges are cut into tiles of 64 in order; a block beyond the last tile leaves.
+//   mode 0 (up):   a row's input is h[pair / top]; out: hid[row][col] = relu(acc)^2 (element type)
+//   mode 1 (down): a row's input is hid[row]; out[pair % top][pair / top][col] = wgt[pair] * acc (float32)
+template <typename A>
+__global__ void __launch_bounds__(256) moe_grouped_gemm_kernel(const A* __restrict__ in, int ldin, const A* __restrict__ w,
+                                                               const int* __restrict__ offsets, const int* __restrict__ pair_of_row,
+                                                               const float* __restrict__ wgt, void* __restrict__ out, int E,
+                                                               int top, int T, int K, int N, int mode) {
+  __shared__ __align__(16) float As[16][64 + 4];
+  __shared__ __align__(16) float Bs[16][64 + 4];
+  __shared__ int src_row[64];
+  __shared__ int tile_info[3];
+  if (threadIdx.x == 0) {
+    int want = blockIdx.x, e = 0, found = -1, r0 = 0, r1 = 0;
+    for (; e < E; e++) {
+      int lo = offsets[e], hi = offsets[e + 1];
+      int nt = (hi - lo + 63) / 64;
+      if (want < nt) { found = e; r0 = lo + want * 64; r1 = min(hi, r0 + 64); break; }
+      want -= nt;
+    }
+    tile_info[0] = found; tile_info[1] = r0; tile_info[2] = r1;
+  }
+  __syncthreads();
+  int e = tile_info[0], r0 = tile_info[1], r1 = tile_info[2];
+  if (e < 0) return;
+  int n_rows = r1 - r0;
+  int col0 = blockIdx.y * 64;
+  if (threadIdx.x < 64) {
+    int r = threadIdx.x;
+    src_row[r] = r < n_rows ? (mode == 0 ? pair_of_row[r0 + r] / top : r0 + r) : -1;
+  }
+  __syncthreads();
+  const A* wexp = w + (size_t)e * N * K;
+  int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;           // columns tx * 4 .., rows ty * 4 ..
+  float acc[4][4];
+#pragma unroll
+  for (int a = 0; a < 4; a++)
+#pragma unroll
+    for (int c = 0; c < 4; c++) acc[a][c] = 0.f;
+  for (int k0 = 0; k0 < K; k0 += 16) {
+    for (int i = threadIdx.x; i < 64 * 16; i += 256) {
+      int r = i >> 4, kk = i & 15;
+      int sr = src_row[r];
+      float av = (sr >= 0 && k0 + kk < K) ? to_f32(in[(size_t)sr * ldin + k0 + kk]) : 0.f;
+      As[kk][r] = av;
+      int cidx = col0 + r;
+      float bv = (cidx < N && k0 + kk < K) ? to_f32(wexp[(size_t)cidx * K + k0 + kk]) : 0.f;
+      Bs[kk][r] = bv;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < 16; kk++) {
+      float4 av = *(const float4*)&As[kk][ty * 4];
+      float4 bv = *(const float4*)&Bs[kk][tx * 4];
+      float a4[4] = {av.x, av.y, av.z, av.w}, b4[4] = {bv.x, bv.y, bv.z, bv.w};
+#pragma unroll
+      for (int a = 0; a < 4; a++)
+#pragma unroll
+        for (int c = 0; c < 4; c++) acc[a][c] += a4[a] * b4[c];
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int a = 0; a < 4; a++) {
+    int r = ty * 4 + a;
+    if (r >= n_rows) continue;
+    if (mode == 0) {
+      A* orow = (A*)out + (size_t)(r0 + r) * N;
+#pragma unroll
+      for (int c = 0; c < 4; c++) {
+        int col = col0 + tx * 4 + c;
+        if (col < N) orow[col] = from_f32<A>(acc[a][c] > 0.f ? acc[a][c] * acc[a][c] : 0.f);
+      }
+    } else {
+      int pr = pair_of_row[r0 + r];
+      float wv = wgt[pr];
+      float* orow = (float*)out + ((size_t)(pr % top) * T + pr / top) * N;
+#pragma unroll
+      for (int c = 0; c < 4; c++) {
+        int col = col0 + tx * 4 + c;
+        if (col < N) orow[col] = wv * acc[a][c];
+      }
+    }
+  }
+}
+
+}  // namespace mix

@@ -1,2 +1,3 @@
 from . import llama  # noqa: F401  (registers LlamaForCausalLM)
 from . import sozilix  # noqa: F401  (registers Sozilix)
+from . import muvorax  # noqa: F401  (registers Muvorax)

@@ -1,4 +1,5 @@
-from . import attention, block, delta_rule, embedding, feedforward, norm, parallel, rglru, rotary  # noqa: F401  (registers the built-in parts)
+from . import (attention, block, delta_rule, embedding, experts, feedforward, latent_attention, linear_attention, norm, parallel, rglru,
+               rotary, selective_scan)  # noqa: F401  (registers the built-in parts)
 from .base import (ARRANGEMENTS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, POSITION_ENCODINGS, Embedding, FeedForward,
                    Head, Mixer, Norm, Part, PartSpec, PositionEncoding)
 from .block import Block, LayerSpec, build_block, pre_norm_layer

@@ -200,7 +200,44 @@ class ScaledPreNormBlock(Block):
         return self._scaled(self.feed_forward.forward(n2, ctx))
 
 
+class SandwichNormBlock(Block):
+    """x += post1(mixer(pre1(x))); then, if the layer has a feed-forward, x += post2(feed_forward(pre2(x))):
+    a norm in front of and behind every sublayer. Roles: `mixer_norm`, `mixer`, `mixer_post_norm`, and
+    all or none of `feed_forward_norm`, `feed_forward`, `feed_forward_post_norm`. The norm behind a
+    sublayer does not run by itself: the sublayer's output goes on as a `NormedAddend`, and the norm
+    that reads the stream next (this layer's second, the next layer's first, or the model's last)
+    applies it while it adds, so the norms named here must take such addends (`dynamic_tanh`)."""
+
+    def __init__(self, spec: LayerSpec):
+        self.mixer_norm = NORMS.build(_role(spec, "mixer_norm"))
+        self.mixer = MIXERS.build(_role(spec, "mixer"))
+        self.mixer_post_norm = NORMS.build(_role(spec, "mixer_post_norm"))
+        roles = ("feed_forward_norm", "feed_forward", "feed_forward_post_norm")
+        has = [r in spec.parts for r in roles]
+        if any(has) and not all(has):
+            raise ValueError("a layer has a feed-forward with a norm on either side, or none of the three")
+        self.feed_forward_norm = NORMS.build(spec.parts[roles[0]]) if has[0] else None
+        self.feed_forward = FEED_FORWARDS.build(spec.parts[roles[1]]) if has[1] else None
+        self.feed_forward_post_norm = NORMS.build(spec.parts[roles[2]]) if has[2] else None
+
+    def parts(self):
+        out = [self.mixer_norm, self.mixer, self.mixer_post_norm]
+        if self.feed_forward is not None:
+            out += [self.feed_forward_norm, self.feed_forward, self.feed_forward_post_norm]
+        return out
+
+    def forward(self, residual, delta, ctx, unit, writes):
+        from .norm import NormedAddend
+        h = self.mixer_norm.forward(residual, delta, ctx)
+        pending = NormedAddend(self.mixer.forward(h, ctx, unit, writes), self.mixer_post_norm)
+        if self.feed_forward is None:
+            return pending
+        h2 = self.feed_forward_norm.forward(residual, pending, ctx)
+        return NormedAddend(self.feed_forward.forward(h2, ctx), self.feed_forward_post_norm)
+
+
 ARRANGEMENTS.register("pre_norm", PreNormBlock)
+ARRANGEMENTS.register("sandwich_norm", SandwichNormBlock)
 ARRANGEMENTS.register("scaled_pre_norm", ScaledPreNormBlock)
 
 

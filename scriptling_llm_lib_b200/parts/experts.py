@@ -1,0 +1,111 @@
+"""Feed-forwards with one activation, dense or routed to a few of many small experts.
+
+`act_feed_forward`: y = Wdown act(Wup x), no gate, no biases; act is the tanh form of gelu, the
+square of relu, or silu.
+
+`routed_experts`: `experts` such feed-forwards (act = relu^2 by default) of which every token uses
+`top`. Router: z = Wr x with float32 sums, s = sigmoid(z); the choice is made on s + correction (a
+stored vector), the weights use s without it. Experts form `n_groups` equal groups of neighbours;
+a group's score is the sum of its two largest choice scores, and only experts of the `keep_groups`
+best groups can be chosen (the others count as minus infinity). The `top` largest choice scores
+win; their weights are s / (sum of the chosen s + 1e-20) * scale. The output is the weighted sum
+of the chosen experts' outputs.
+
+The experts' matrices are stacked [experts, ff, hidden] and [experts, hidden, ff]. A step of few
+rows runs every (token, chosen expert) pair by itself (each streams its expert's matrices once); a
+longer step groups the pairs by expert on the device and runs tiles of rows per expert. Both
+launch the same work whatever the router chose, so a decode step can be captured. The weighted
+outputs leave as float32 partial sums [top, T, hidden], one per choice, which the next reader of
+the residual stream adds in a fixed order.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..weights.spec import TensorSpec
+from .base import FEED_FORWARDS, FeedForward
+from .linear import Linear
+
+ACTS = ("gelu_tanh", "relu_squared", "silu")
+
+
+class ActFeedForward(FeedForward):
+    graph_safe = True
+
+    def __init__(self, hidden: int, intermediate: int, up_name: str, down_name: str, act: str = "gelu_tanh"):
+        if act not in ACTS:
+            raise ValueError(f"activation {act!r}; known: {', '.join(ACTS)}")
+        self.hidden, self.intermediate, self.act = hidden, intermediate, act
+        self.up = Linear([up_name], [intermediate], hidden)
+        self.down = Linear([down_name], [hidden], intermediate)
+
+    def tensor_specs(self):
+        return self.up.tensor_specs() + self.down.tensor_specs()
+
+    def bind(self, tensors, dtype, device):
+        self.up.bind(tensors, dtype, device)
+        self.down.bind(tensors, dtype, device)
+
+    def forward(self, x, ctx):
+        h = self.up.forward(x, ctx)
+        ctx.kernels.mix.act_inplace(h, self.act)
+        return self.down.forward(h, ctx, partials_ok=True)
+
+
+class RoutedExperts(FeedForward):
+    graph_safe = True
+    PAIRS_ONE_BY_ONE = 64        # up to this many (token, expert) pairs in a step each pair runs by itself
+
+    def __init__(self, hidden: int, intermediate: int, experts: int, top: int, n_groups: int, keep_groups: int, scale: float,
+                 router_name: str, correction_name: str, up_names: list, down_names: list, act: str = "relu_squared"):
+        if act != "relu_squared":
+            raise ValueError("the experts' kernels apply the square of relu")
+        if len(up_names) != experts or len(down_names) != experts:
+            raise ValueError(f"{experts} experts need as many up and down matrices")
+        if n_groups < 1 or experts % n_groups or not 1 <= keep_groups <= n_groups:
+            raise ValueError(f"{experts} experts cannot form {n_groups} equal groups of which {keep_groups} are kept")
+        if not 1 <= top <= keep_groups * (experts // n_groups):
+            raise ValueError(f"{top} experts a token cannot come out of {keep_groups} groups of {experts // n_groups}")
+        self.hidden, self.F, self.E, self.top = hidden, intermediate, experts, top
+        self.n_groups, self.keep, self.scale = n_groups, keep_groups, float(scale)
+        self.router_name, self.correction_name = router_name, correction_name
+        self.up_names, self.down_names = list(up_names), list(down_names)
+
+    def tensor_specs(self):
+        specs = [TensorSpec(self.router_name, (self.E, self.hidden)), TensorSpec(self.correction_name, (self.E,), init="bias")]
+        for u, d in zip(self.up_names, self.down_names):
+            specs += [TensorSpec(u, (self.F, self.hidden)), TensorSpec(d, (self.hidden, self.F))]
+        return specs
+
+    def elements_read_per_step(self) -> int:
+        """A decode step reads the router and, per token, `top` experts: counted once (one token)."""
+        return self.E * self.hidden + self.E + self.top * 2 * self.F * self.hidden
+
+    def bind(self, tensors, dtype, device):
+        self.router = tensors[self.router_name]
+        self.correction = tensors[self.correction_name].float().contiguous()
+        self.w_up = torch.stack([tensors[n] for n in self.up_names]).contiguous()        # [E, F, hidden]
+        self.w_down = torch.stack([tensors[n] for n in self.down_names]).contiguous()    # [E, hidden, F]
+        self.counts = torch.zeros((self.E,), dtype=torch.int32, device=device)
+        if self.router.dtype != dtype or self.w_up.dtype != dtype:
+            raise ValueError(f"the experts' matrices are {self.w_up.dtype}, the engine runs in {dtype}")
+
+    def forward(self, x, ctx):
+        k = ctx.kernels.mix
+        T, dev = x.shape[0], x.device
+        idx = torch.empty((T, self.top), dtype=torch.int32, device=dev)
+        wgt = torch.empty((T, self.top), dtype=torch.float32, device=dev)
+        k.moe_route(x, self.router, self.correction, idx, wgt, self.n_groups, self.keep, self.top, self.scale)
+        hid = torch.empty((T * self.top, self.F), dtype=x.dtype, device=dev)
+        out = torch.empty((self.top, T, self.hidden), dtype=torch.float32, device=dev)
+        if T * self.top <= self.PAIRS_ONE_BY_ONE:
+            k.moe_pairs(x, self.w_up, self.w_down, idx, wgt, hid, out)
+        else:
+            offsets = torch.empty((self.E + 1,), dtype=torch.int32, device=dev)
+            pair_of_row = torch.empty((T * self.top,), dtype=torch.int32, device=dev)
+            k.moe_grouped(x, self.w_up, self.w_down, idx, wgt, self.counts, offsets, pair_of_row, hid, out)
+        return out
+
+
+FEED_FORWARDS.register("act_feed_forward", ActFeedForward)
+FEED_FORWARDS.register("routed_experts", RoutedExperts)

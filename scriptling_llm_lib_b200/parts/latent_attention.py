@@ -1,0 +1,108 @@
+"""Causal softmax attention whose keys and values are made from a cached latent.
+
+From the mixer's input h: q = Wq h, per head [dim unrotated | rot_dim rotated] dims. Wdkv h has
+kv_rank + rot_dim rows: the first kv_rank, divided by their root mean square and multiplied by a
+weight, are the latent c; the last rot_dim are a key part that all heads share. Head i's key is
+[Wuk_i c | shared part], its value Wuv_i c; the score is (q . k) * scale, the mask causal, the
+softmax ordinary, and Wo maps the heads' outputs back. A position encoding (a rotation by a table)
+turns the rot_dim part of every query head and the shared key part; values are not turned.
+
+Only c and the rotated key part are cached: one vector of kv_rank + rot_dim per position, whatever
+the number of heads (a cache unit with one key "head" of that width and no value storage). Keys
+and values are never formed per position. Since q_i . (Wuk_i c) = (Wuk_i^T q_i) . c, a head asks
+the cached vectors with [Wuk_i^T q_i | q_rot] directly, sums the latents with the softmax weights,
+and applies Wuv_i once to that sum. All heads of a row read the same cached rows.
+
+A layer built with `shares_cache=True` has no Wdkv: it runs with `writes=False` on the unit another
+latent-attention layer of the same widths and rotation wrote, with its own Wq, Wuk, Wuv and Wo.
+
+The products run in the engine's dtype and the cache holds it; the latent's norm, the rotation,
+the absorbed queries, scores, softmax and sums over the latent are float32.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..cache.needs import PAGE, CacheNeed
+from ..weights.spec import TensorSpec
+from .base import MIXERS, POSITION_ENCODINGS, Mixer, PartSpec
+from .linear import Linear
+
+
+class LatentAttention(Mixer):
+    graph_safe = True
+    MAX_RANK = 1024          # the kernel keeps a lane's share of the latent sum in registers
+
+    def __init__(self, hidden: int, n_heads: int, dim: int, rot_dim: int, v_dim: int, kv_rank: int, scale: float,
+                 position: PartSpec | None, norm_eps: float, q_name: str, uk_name: str, uv_name: str, o_name: str,
+                 dkv_name: str | None = None, dkv_norm_name: str | None = None, shares_cache: bool = False):
+        if kv_rank < 1 or kv_rank > self.MAX_RANK:
+            raise ValueError(f"latent of width {kv_rank}: the attention kernel takes 1..{self.MAX_RANK}")
+        if not shares_cache and (dkv_name is None or dkv_norm_name is None):
+            raise ValueError("a latent-attention layer with a cache of its own needs the down-projection and its norm weight")
+        self.hidden, self.H, self.D, self.P, self.V, self.R = hidden, n_heads, dim, rot_dim, v_dim, kv_rank
+        self.scale, self.eps, self.shares_cache = float(scale), float(norm_eps), bool(shares_cache)
+        self.position = POSITION_ENCODINGS.build(position) if position is not None else None
+        qw = n_heads * (dim + rot_dim)
+        self.q_width = qw
+        if shares_cache:
+            self.proj = Linear([q_name], [qw], hidden)
+        else:
+            self.proj = Linear([q_name, dkv_name], [qw, kv_rank + rot_dim], hidden)
+        self.out = Linear([o_name], [hidden], n_heads * v_dim)
+        self.uk_name, self.uv_name, self.dkv_norm_name = uk_name, uv_name, dkv_norm_name
+
+    def tensor_specs(self):
+        specs = self.proj.tensor_specs() + self.out.tensor_specs() + [
+            TensorSpec(self.uk_name, (self.H * self.D, self.R)), TensorSpec(self.uv_name, (self.H * self.V, self.R))]
+        if not self.shares_cache:
+            specs.append(TensorSpec(self.dkv_norm_name, (self.R,), init="norm_weight"))
+        return specs
+
+    def bind(self, tensors, dtype, device):
+        self.proj.bind(tensors, dtype, device)
+        self.out.bind(tensors, dtype, device)
+        self.wuk, self.wuv = tensors[self.uk_name], tensors[self.uv_name]
+        self.norm_w = None if self.shares_cache else tensors[self.dkv_norm_name].float().contiguous()
+
+    def prepare(self, max_positions, device):
+        if self.position is not None:
+            self.position.prepare(max_positions, device)
+
+    def cache_need(self):
+        return CacheNeed("full", 1, self.R + self.P, None, v_dim=0)
+
+    def splits(self, ctx) -> int:
+        """Over how many blocks a row's keys are split: one in a prompt step (its rows fill the GPU), in a
+        decode step enough for about two blocks per SM, at most one per 32 keys of the longest sequence."""
+        if not ctx.is_decode:
+            return 1
+        blocks = ctx.n_seqs * -(-self.H // 8)
+        return max(1, min(-(-2 * ctx.engine.sm_count // blocks), ctx.max_pages * PAGE // 32, 64))
+
+    def forward(self, x, ctx, unit, writes):
+        if writes == self.shares_cache:
+            raise ValueError("a latent-attention layer writes the cache unit exactly when it has a down-projection of its own")
+        k = ctx.kernels.mix
+        pages, _, block_table = ctx.unit_kv(unit)
+        T = x.shape[0]
+        proj = self.proj.forward(x, ctx)                                         # [T, q (| latent and key part, raw)]
+        q = proj[:, :self.q_width]
+        table, rot = None, 0
+        if self.position is not None:
+            table, rot, interleaved = self.position.rotation()
+            if not interleaved:
+                raise ValueError("latent attention rotates adjacent pairs")
+        k.latent_store(q, self.H, self.D, proj[:, self.q_width:] if writes else None, self.norm_w, self.eps, table, rot, ctx,
+                       block_table, pages if writes else None, self.R, self.P)
+        qa = torch.empty((T, self.H, self.R + self.P), dtype=torch.float32, device=x.device)
+        k.latent_absorb(q, self.wuk, qa, self.H, self.D, self.P, self.R, self.scale)
+        n_split = self.splits(ctx)
+        part = torch.empty((T, self.H, n_split, self.R + 2), dtype=torch.float32, device=x.device)
+        k.latent_attn(qa, pages, ctx, block_table, part, self.H, self.R, self.P, n_split)
+        attn = torch.empty((T, self.H * self.V), dtype=x.dtype, device=x.device)
+        k.latent_expand(part, self.wuv, attn, self.H, self.V, self.R, n_split)
+        return self.out.forward(attn, ctx, partials_ok=True)
+
+
+MIXERS.register("latent_attention", LatentAttention)

@@ -8,6 +8,9 @@ from __future__ import annotations
 
 import torch
 
+from dataclasses import dataclass
+from typing import Any
+
 from ..weights.spec import TensorSpec
 from .base import NORMS, Folded, Norm
 
@@ -74,5 +77,53 @@ class WeightedNorm(Norm):
         return y
 
 
+@dataclass
+class NormedAddend:
+    """A sublayer's output that passes a norm of its own before it joins the residual stream:
+    x += norm(y). `y` is [T, width] (the engine's dtype or float32) or float32 [P, T, width] partial
+    sums; `norm` is the part that owns weight, bias and slope. The norm that reads the stream next
+    applies it while it forms the sum, so the addend is read once and never stored normed."""
+    y: Any
+    norm: "DynamicTanh"
+
+
+class DynamicTanh(Norm):
+    """A norm that takes no statistics of the row: y = tanh(alpha * v) * w + b, alpha one number,
+    w and b vectors, every element on its own in float32. In front of a sublayer it reads
+    v = residual + pending addend (the sum is kept); behind a sublayer it is only named in a
+    `NormedAddend`, and the next reader of the stream does the work of both in one pass."""
+    graph_safe = True
+
+    def __init__(self, width: int, weight_name: str, bias_name: str, alpha_name: str):
+        self.width, self.weight_name, self.bias_name, self.alpha_name = width, weight_name, bias_name, alpha_name
+        self.weight = self.bias = None
+        self.alpha = 1.0
+
+    def tensor_specs(self):
+        return [TensorSpec(self.weight_name, (self.width,), init="norm_weight"), TensorSpec(self.bias_name, (self.width,), init="bias"),
+                TensorSpec(self.alpha_name, (), init="slope")]
+
+    def elements_read_per_step(self) -> int:
+        return 2 * self.width
+
+    def bind(self, tensors, dtype, device):
+        self.weight = tensors[self.weight_name].float().contiguous()
+        self.bias = tensors[self.bias_name].float().contiguous()
+        self.alpha = float(tensors[self.alpha_name].float().cpu())
+
+    def terms(self):
+        return self.weight, self.bias, self.alpha
+
+    def forward(self, residual, delta, ctx, rows=None):
+        addend, post = delta, None
+        if isinstance(delta, NormedAddend):
+            addend, post = delta.y, delta.norm.terms()
+        n = residual.shape[0] if rows is None else rows.shape[0]
+        y = torch.empty((n, self.width), dtype=ctx.dtype, device=residual.device)
+        ctx.kernels.mix.dyt_add_norm(residual, addend, post, rows, self.weight, self.bias, self.alpha, y)
+        return y
+
+
 NORMS.register("rmsnorm", RMSNorm)
+NORMS.register("dynamic_tanh", DynamicTanh)
 NORMS.register("weighted_norm", WeightedNorm)

@@ -12,11 +12,30 @@ is the mixer's business: V is never rotated, model_f32.go:445-448).
 from __future__ import annotations
 
 import math
+from dataclasses import dataclass
 
 import numpy as np
 import torch
 
 from .base import POSITION_ENCODINGS, PositionEncoding
+
+
+@dataclass(frozen=True)
+class YarnScaling:
+    """Stretching of a rotation to longer sequences that leaves fast pairs alone: pair i has
+    index(t) = dims * ln(original / (2 pi t)) / (2 ln theta) as the pair that makes t turns over the
+    original length; pairs below index(fast) keep their frequency, pairs above index(slow) are slowed
+    down by `factor`, a linear ramp over the pair index joins the two, and cos and sin are
+    multiplied by 0.1 ln(factor) + 1."""
+    factor: float
+    original: float
+    fast: float
+    slow: float
+    rope_type: str = "yarn"
+
+    @property
+    def amplitude(self) -> float:
+        return 0.1 * math.log(self.factor) + 1.0
 
 
 def inverse_frequencies(rotary_dim: int, theta: float, scaling=None) -> np.ndarray:
@@ -34,6 +53,13 @@ def inverse_frequencies(rotary_dim: int, theta: float, scaling=None) -> np.ndarr
             scaling.high_freq_factor - scaling.low_freq_factor)
         blended = (1.0 - smooth) * f / scaling.factor + smooth * f
         return np.where(wavelen > lo_wavelen, f / scaling.factor, np.where(wavelen < hi_wavelen, f, blended))
+    if scaling.rope_type == "yarn":
+        def index(turns):
+            return rotary_dim * math.log(scaling.original / (2.0 * math.pi * turns)) / (2.0 * math.log(float(theta)))
+        lo = max(math.floor(index(scaling.fast)), 0)
+        hi = min(math.ceil(index(scaling.slow)), rotary_dim - 1)
+        ramp = np.clip((i - lo) / max(hi - lo, 0.001), 0.0, 1.0)
+        return f / scaling.factor * ramp + f * (1.0 - ramp)
     raise ValueError(f"unknown rope scaling {scaling.rope_type!r}")
 
 
@@ -45,13 +71,14 @@ class RotaryEncoding(PositionEncoding):
             raise ValueError(f"rotary width {rotary_dim} must be even and within 2..{head_dim}")
         self.head_dim, self.rotary_dim, self.theta, self.scaling, self.pairing = head_dim, rotary_dim, theta, scaling, pairing
         self.inv_freq = inverse_frequencies(rotary_dim, theta, scaling)
+        self.amplitude = float(getattr(scaling, "amplitude", 1.0)) if scaling is not None else 1.0
         self.cos_sin: torch.Tensor | None = None     # [positions, rotary_dim/2, 2] float32
 
     def prepare(self, max_positions: int, device) -> None:
         if self.cos_sin is not None and self.cos_sin.shape[0] >= max_positions and self.cos_sin.device == torch.device(device):
             return
         ang = np.arange(max_positions, dtype=np.float64)[:, None] * self.inv_freq[None, :]
-        table = np.stack([np.cos(ang), np.sin(ang)], axis=-1).astype(np.float32)
+        table = (np.stack([np.cos(ang), np.sin(ang)], axis=-1) * self.amplitude).astype(np.float32)
         self.cos_sin = torch.from_numpy(table).to(device).contiguous()
 
     @property

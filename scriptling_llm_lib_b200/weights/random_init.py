@@ -55,6 +55,7 @@ INIT_LAWS: dict[str, Normal | UniformInteger] = {
     "bias": Normal(0.0, 0.1),
     "log_rate": Normal(0.0, 0.5),           # logarithms of decay rates (a recurrence's A_log, lambda)
     "gate_matrix": Normal(0.0, 0.05),       # the small square blocks of block-diagonal gates
+    "slope": Normal(1.0, 0.1),              # the one number inside a norm's tanh
 }
 
 
