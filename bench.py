@@ -465,27 +465,69 @@ def sozilix_config(z):
             "residual_mult": 1.0, "vocab": DESIGN_VOCAB, "width": z["width"]}
 
 
-def llama_like(z, max_positions):
-    return {"architectures": ["LlamaForCausalLM"], "model_type": "llama", "num_hidden_layers": 3 * z["groups"],
+# The Muvorax decoder (latent attention, the selective scan and decayed linear attention, each with routed experts
+# but for a dense first layer) at layer sizes that resemble real models of its kinds: a latent of 512 (256) with 128 + 64
+# query/key dims a head, scan channels of twice the width with 16 states, linear-attention heads of 128 x 128,
+# 64 (32) experts of which 6 (4) are used. The Llama decoder beside it has the same width, depth, heads and the
+# dense layer's feed-forward in every layer.
+MUVORAX_SIZES = {
+    "w1024": dict(width=1024, heads=8, kv_heads=2, dim=128, vdim=128, rot_dim=64, rank=256, ff=4096, experts=32, top=4, n_groups=4,
+                  keep=2, expert_ff=704, groups=1),
+    "w2048": dict(width=2048, heads=16, kv_heads=4, dim=128, vdim=128, rot_dim=64, rank=512, ff=8192, experts=64, top=6, n_groups=8,
+                  keep=3, expert_ff=1408, groups=1),
+}
+
+
+def muvorax_config(z):
+    W, H = z["width"], z["heads"]
+    rot = {"base": 10000.0, "dims": z["rot_dim"], "scaling": {"factor": 40.0, "fast": 32.0, "original": 4096, "slow": 1.0}}
+    moe = {"expert": {"ff": z["expert_ff"]}, "kind": "moe", "router": {
+        "experts": z["experts"], "groups": {"count": z["n_groups"], "keep": z["keep"]}, "scale": 2.5, "top": z["top"]}}
+
+    def latent(src=None):
+        m = {"dim": z["dim"], "heads": H, "kv_rank": z["rank"], "rot": rot, "rot_dim": z["rot_dim"],
+             "scale": (z["dim"] + z["rot_dim"]) ** -0.5, "vdim": z["vdim"]}
+        if src is not None:
+            m["kv_from"] = src
+        return m
+    scan = {"conv": 4, "dt_rank": W // 16, "inner": 2 * W, "state": 16}
+    lin = {"decay": [1.0 - 2.0 ** (-5 - 3 * h / max(1, H - 1)) for h in range(H)], "dim": 128, "heads": W // 128, "vdim": 128}
+    lin["decay"] = lin["decay"][:lin["heads"]] + [0.99] * max(0, lin["heads"] - H)
+    layers = []
+    for g in range(z["groups"]):
+        first = 6 * g
+        layers += [{"type": "latent_attention", "mixer": latent(), "mlp": {"ff": z["ff"], "kind": "dense"} if g == 0 else moe},
+                   {"type": "mamba1", "mixer": scan, "mlp": moe}, {"type": "lightning", "mixer": lin, "mlp": moe},
+                   {"type": "latent_attention", "mixer": latent(first), "mlp": moe}, {"type": "lightning", "mixer": lin, "mlp": moe},
+                   {"type": "mamba1", "mixer": scan, "mlp": moe}]
+    return {"architecture": "Muvorax", "layers": layers, "norm": {"eps": 1e-6}, "vocab": DESIGN_VOCAB, "width": W}
+
+
+DESIGNS = {"sozilix": (DESIGN_SIZES, sozilix_config, 3), "muvorax": (MUVORAX_SIZES, muvorax_config, 6)}
+
+
+def llama_like(z, max_positions, layers_per_group=3):
+    return {"architectures": ["LlamaForCausalLM"], "model_type": "llama", "num_hidden_layers": layers_per_group * z["groups"],
             "hidden_size": z["width"], "num_attention_heads": z["heads"], "num_key_value_heads": z["kv_heads"],
             "head_dim": max(z["dim"], z["vdim"]), "intermediate_size": z["ff"], "vocab_size": DESIGN_VOCAB, "rope_theta": 10000.0,
             "rms_norm_eps": 1e-5, "tie_word_embeddings": False, "max_position_embeddings": max_positions,
-            "sliding_window": z["window"], "hidden_act": "silu"}
+            "sliding_window": z.get("window"), "hidden_act": "silu"}
 
 
 def design_compare(args):
-    """Prompt-step and decode throughput of the Sozilix decoder at DESIGN_SIZES beside the Llama decoder of
-    equal size (random weights, bfloat16 unless --dtype says otherwise); one JSON line."""
+    """Prompt-step and decode throughput of the design named by --design at its sizes beside the Llama decoder
+    of equal size (random weights, bfloat16 unless --dtype says otherwise); one JSON line."""
+    sizes, make_config, per_group = DESIGNS[args.design]
     pk = peaks()
     tmp = tempfile.mkdtemp(prefix="sllm_bench_")
     b = Bench(args, pk, tmp)
     out = {"metric": "design_compare", "design": args.design, "dtype": args.dtype, "data": "synthetic, random weights",
            "prefill_tokens": args.prefill_tokens, "decode": {"batch": args.batch, "context": args.context, "steps": args.steps,
                                                              "warmup": args.warmup}, "sizes": {}}
-    for name in (args.design_sizes.split(",") if args.design_sizes else DESIGN_SIZES):
-        z = DESIGN_SIZES[name]
+    for name in (args.design_sizes.split(",") if args.design_sizes else sizes):
+        z = sizes[name]
         rec = {}
-        for which, raw in (("sozilix", sozilix_config(z)), ("llama", llama_like(z, args.context + args.prefill_tokens + 64))):
+        for which, raw in ((args.design, make_config(z)), ("llama", llama_like(z, args.context + args.prefill_tokens + 64, per_group))):
             path = os.path.join(tmp, f"{name}-{which}.json")
             with open(path, "w") as f:
                 json.dump(raw, f)
@@ -737,7 +779,7 @@ def main():
     ap.add_argument("--kernel", default=None, choices=["attn_decode", "gemm_small_m", "sequence"],
                     help="time one decode kernel alone at --shape, --batch (and --context) instead of the model; 'sequence': "
                          "the kernels of the mixers with state at --design-sizes, for a prompt and for a decode step")
-    ap.add_argument("--design", default=None, choices=["sozilix"],
+    ap.add_argument("--design", default=None, choices=sorted(DESIGNS),
                     help="measure this design's prompt step and decoding at a few real layer sizes beside the Llama decoder "
                          "of equal size (--prefill-tokens, --batch, --context, --steps, --dtype, --only apply) instead of the "
                          "headline run")

@@ -282,20 +282,34 @@ def test_long_decoding_keeps_the_states(folders):
 
 # --------------------------------------------------------------------------- far keys and page borders
 def test_one_loud_key_far_back_and_at_page_borders(tmp_path):
-    """A softmax so sharp that one key carries the row: the rows after position p ask for the latent
-    cached at p, for p far back, on either side of a page border and at the first position; in a
-    prompt and token by token."""
-    cfg = config([with_ff(latent(2, 8, 4, 8, 12, 6.0, 50.0), dense(32))], width=32, vocab=40)
+    """One key that carries every later row. A token of its own (the last id) lights channel 0 of the
+    stream, the down-projection turns that into the latent's first component, head 0's first key dim
+    reads it, and every query has a constant there: so wherever that token stands, at the first
+    position, far back, or on either side of a page border, the rows behind it take their output from
+    its cached latent; in a prompt and token by token."""
+    cfg = config([with_ff(latent(2, 8, 4, 8, 12, 2.0, 50.0), dense(32))], width=32, vocab=40)
     W = random_weights(cfg, 7, std=0.5)
+    loud = 39
+    W["embed"][:, 0] = 0.0
+    W["embed"][loud, 0] = 8.0
+    for name, v0, v1 in (("l0.norm1", 1.0, 0.0), ("l0.norm1.b", 0.0, 1.0)):       # channel 0 passes, channel 1 is the constant 1
+        W[name][0], W[name][1] = v0, v1
+    W["l0.mix.dkv"][0, :] = 0.0
+    W["l0.mix.dkv"][0, 0] = 10.0
+    W["l0.mix.dkv.norm"][0] = 1.0
+    W["l0.mix.uk"][0, :] = 0.0
+    W["l0.mix.uk"][0, 0] = 1.0
+    W["l0.mix.q"][0, :] = 0.0
+    W["l0.mix.q"][0, 1] = 5.0
     folder = write_folder(tmp_path / "m", cfg, W)
     eng = engine(folder)
-    base = ids(200, 40, 16)
+    base = ids(200, 39, 16)                          # never the loud token
+    other = plain_logits(cfg, W, base)
     for p in (0, 1, 63, 64, 65, 127, 128, 150):
         tokens = list(base)
-        tokens[p] = (tokens[p] + 7) % 40
+        tokens[p] = loud
         want = plain_logits(cfg, W, tokens)
-        other = plain_logits(cfg, W, base)
-        assert rel(want[190:], other[190:]) > 10 * TOL_F32          # the far key shows in the last rows
+        assert rel(want[190:], other[190:]) > 100 * TOL_F32         # the far key shows in the last rows
         assert rel(run(eng, [tokens]), want) < TOL_F32
         assert rel(run(eng, [tokens[:170]] + [[t] for t in tokens[170:]]), want) < TOL_F32
 
