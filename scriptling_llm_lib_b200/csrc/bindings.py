@@ -338,6 +338,20 @@ class TensorCoreGemm:
 
     SKINNY_MAX_M = 128
 
+    def gemm_grouped(self, a, w, out, tile_group, err_flag):
+        """out[M, N] = a[M, K] @ w[g]^T with w [G, N, K] and the 128 rows of `a` from row 128 t on multiplied by
+        matrix tile_group[t] (int32 on the device, M / 128 entries): rows laid out so that no 128 hold two groups."""
+        M, K = a.shape
+        G, N = w.shape[0], w.shape[1]
+        if (w.dim() != 3 or w.shape[2] != K or tuple(out.shape) != (M, N) or a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16
+                or out.dtype not in (torch.bfloat16, torch.float32) or tile_group.shape[0] * 128 < M):
+            raise KernelError(f"gemm_grouped shapes: a {tuple(a.shape)} {a.dtype}, w {tuple(w.shape)}, out {tuple(out.shape)} {out.dtype}")
+        fn = self.lib.sllm_gemm_tc_grouped_bf16
+        fn.restype = c_int
+        _check(fn(_ptr(a, torch.bfloat16, "a"), _ptr(w, torch.bfloat16, "w"), _ptr(out, None, "out"), c_int(M), c_int(N), c_int(K),
+                  c_int(K), c_int(K), c_int(N), c_int(1 if out.dtype == torch.float32 else 0), _ptr(tile_group, torch.int32, "tile_group"),
+                  c_int(G), _ptr(err_flag, torch.int32, "err_flag"), _stream()), "gemm_grouped")
+
     def gemm_skinny(self, a, w, out, err_flag, swiglu=False):
         """The same product for at most 128 rows of `a`, with the weights as the tensor cores' 128-row
         operand and a grid over (128 weight rows, K splits). out [M,N] bfloat16 or float32, or
@@ -834,17 +848,44 @@ class MixKernels:
                                      _ptr(hid, self.dtype, "hid"), _ptr(out, torch.float32, "out"), c_int(T), c_int(top), c_int(K),
                                      c_int(wup.shape[1]), c_int(wdown.shape[1]), _stream()), "moe_pairs")
 
-    def moe_grouped(self, h, wup, wdown, idx, wgt, counts, offsets, pair_of_row, hid, out):
-        """The same over pairs grouped by expert (a prompt step). counts int32 [E] must be zero and is left zero."""
+    def moe_group_rows(self, idx, counts, offsets, pair_of_row, row_of_pair=None, tile_group=None, pad=1):
+        """Groups the (token, expert) pairs of idx [T, top] by expert. counts int32 [E] must be zero and is left
+        zero; offsets int32 [E + 1] the experts' first rows; pair_of_row int32 [rows] (-1: no pair); row_of_pair
+        int32 [T * top] the inverse. pad > 1: every expert's rows start at a multiple of pad, and
+        tile_group int32 [rows / pad] names the expert of every pad rows."""
+        T, top = idx.shape
+        _check(self._fn("moe_group_rows")(_ptr(idx, torch.int32, "idx"), _ptr(counts, torch.int32, "counts"),
+                                          _ptr(offsets, torch.int32, "offsets"), _ptr(pair_of_row, torch.int32, "pair_of_row"),
+                                          _ptr(row_of_pair, torch.int32, "row_of_pair"), _ptr(tile_group, torch.int32, "tile_group"),
+                                          c_int(T), c_int(top), c_int(counts.shape[0]), c_int(pad), c_int(pair_of_row.shape[0]),
+                                          _stream()), "moe_group_rows")
+        LAUNCHES[0] += 4
+
+    def moe_grouped(self, h, wup, wdown, wgt, offsets, pair_of_row, hid, out):
+        """The experts' products over rows grouped without padding (`moe_group_rows` with pad 1), float32 sums on
+        the FMA units; out float32 [top, T, N]."""
         T, K = h.shape
-        top = idx.shape[1]
+        top = wgt.shape[1]
         _check(self._fn("moe_grouped")(self._view(h, "h"), c_int(h.stride(0)), _ptr(wup, self.dtype, "wup"),
-                                       _ptr(wdown, self.dtype, "wdown"), _ptr(idx, torch.int32, "idx"),
-                                       _ptr(wgt, torch.float32, "wgt"), _ptr(counts, torch.int32, "counts"),
+                                       _ptr(wdown, self.dtype, "wdown"), _ptr(wgt, torch.float32, "wgt"),
                                        _ptr(offsets, torch.int32, "offsets"), _ptr(pair_of_row, torch.int32, "pair_of_row"),
                                        _ptr(hid, self.dtype, "hid"), _ptr(out, torch.float32, "out"), c_int(T), c_int(top),
                                        c_int(wup.shape[0]), c_int(K), c_int(wup.shape[1]), c_int(wdown.shape[1]), _stream()),
                "moe_grouped")
+        LAUNCHES[0] += 1
+
+    def moe_gather_rows(self, h, pair_of_row, top, xs):
+        """xs[row] = h[pair_of_row[row] // top], zeros where a row holds no pair."""
+        _check(self._fn("moe_gather_rows")(self._view(h, "h"), c_int(h.stride(0)), _ptr(pair_of_row, torch.int32, "pair_of_row"),
+                                           c_int(top), _ptr(xs, self.dtype, "xs"), c_int(xs.shape[0]), c_int(xs.shape[1]), _stream()),
+               "moe_gather_rows")
+
+    def moe_combine(self, ys, row_of_pair, wgt, out):
+        """out[t] = sum_k wgt[t, k] * ys[row_of_pair[t * top + k]], float32 [T, N]."""
+        T, top = wgt.shape
+        _check(self._fn("moe_combine")(_ptr(ys, torch.float32, "ys"), _ptr(row_of_pair, torch.int32, "row_of_pair"),
+                                       _ptr(wgt, torch.float32, "wgt"), _ptr(out, torch.float32, "out"), c_int(T), c_int(top),
+                                       c_int(out.shape[1]), _stream()), "moe_combine")
 
 
 class CastKernels:

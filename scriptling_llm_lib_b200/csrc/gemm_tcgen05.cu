@@ -45,6 +45,10 @@ struct TcFold {
   const float* norm_w;
   bf16* xb;
   float* sumsq_out;
+  // grouped rows (the one-SM kernel only): B holds `group_rows`-row matrices one under the other, and the 128 rows
+  // of A from row 128 t on are multiplied by matrix tile_group[t]. Null: one matrix for all rows.
+  const int* tile_group;
+  int group_rows;
 };
 
 // the scale a row is owed by a folded norm before the product: its partial sums added in their order
@@ -376,6 +380,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       bool ok = true;
       for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
         int m0 = (tile % tiles_m) * TC_BM, n0 = (tile / tiles_m) * BN;
+        int b_row = n0 + (fd.tile_group ? fd.tile_group[tile % tiles_m] * fd.group_rows : 0);     // the row tile's own matrix
         for (int kb = 0; kb < nkb; kb++, it++) {
           int s = it % STAGES;
           uint32_t ph = (it / STAGES) & 1;
@@ -384,7 +389,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
           uint32_t a_dst = smem_base + s * STAGE_BYTES;
           tma_load_2d(a_dst, &map_a, kb * TC_BK, m0, full0 + 8 * s);
-          tma_load_2d(a_dst + A_BYTES, &map_b, kb * TC_BK, n0, full0 + 8 * s);
+          tma_load_2d(a_dst + A_BYTES, &map_b, kb * TC_BK, b_row, full0 + 8 * s);
         }
       }
       if (*abort) {
@@ -695,6 +700,30 @@ SLLM_EXPORT int sllm_gemm_tc_fold_bf16(const void* A, const void* B, void* C, in
   if (epilogue == TC_EPI_SWIGLU)
     return big ? tc_launch<256, 4, TC_EPI_SWIGLU>(ma, mb, C, M, N, K, ldc, 0, err, stream, rp, fd)
                : tc_launch<128, 6, TC_EPI_SWIGLU>(ma, mb, C, M, N, K, ldc, 0, err, stream, rp, fd);
+  return big ? tc_launch<256, 4, TC_EPI_STORE>(ma, mb, C, M, N, K, ldc, out_f32, err, stream, rp, fd)
+             : tc_launch<128, 6, TC_EPI_STORE>(ma, mb, C, M, N, K, ldc, out_f32, err, stream, rp, fd);
+}
+
+// Grouped rows: C[M,N] = A[M,K] B_g^T with B [n_groups * N, K] holding one [N, K] matrix per group and the 128 rows
+// of A from row 128 t on multiplied by matrix tile_group[t] (int32 on the device, ceil(M / 128) entries, each in
+// 0 .. n_groups - 1). The caller lays the rows of A out so that no tile holds rows of two groups. The one-SM kernel
+// (tiles of 128 rows); a tile's columns beyond N read the next group's rows and are not written.
+SLLM_EXPORT int sllm_gemm_tc_grouped_bf16(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb, int ldc,
+                                          int out_f32, const int* tile_group, int n_groups, int* err, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (K <= 0 || (K & 7) || (lda & 7) || (ldb & 7) || ((uintptr_t)A & 15) || ((uintptr_t)B & 15) || !tile_group || n_groups < 1)
+    return SLLM_ERR_ARG;
+  if ((long long)n_groups * N > 0x7fffffffLL) return SLLM_ERR_ARG;
+  TcFold fd{};
+  fd.tile_group = tile_group;
+  fd.group_rows = N;
+  const TcRope rp{};
+  CUtensorMap ma, mb;
+  int big = N > 128;
+  int rc = tc_make_map(&ma, A, M, K, lda, TC_BM);
+  if (rc) return rc;
+  rc = tc_make_map(&mb, B, n_groups * N, K, ldb, big ? 256 : 128);
+  if (rc) return rc;
   return big ? tc_launch<256, 4, TC_EPI_STORE>(ma, mb, C, M, N, K, ldc, out_f32, err, stream, rp, fd)
              : tc_launch<128, 6, TC_EPI_STORE>(ma, mb, C, M, N, K, ldc, out_f32, err, stream, rp, fd);
 }

@@ -657,23 +657,61 @@ __global__ void moe_count_kernel(const int* __restrict__ idx, int n_pairs, int* 
   int p = blockIdx.x * blockDim.x + threadIdx.x;
   if (p < n_pairs) atomicAdd(&counts[idx[p]], 1);
 }
-__global__ void moe_offsets_kernel(int* __restrict__ counts, int* __restrict__ offsets, int E) {
+// offsets[e]: the first grouped row of expert e, every expert's range rounded up to a multiple of `pad` rows (1: none;
+// offsets[E]: the end). With tile_group: tile_group[t] = the expert whose range holds rows t * pad .. (the last expert
+// with rows for the tiles behind all ranges: they hold no pair).
+__global__ void moe_offsets_kernel(int* __restrict__ counts, int* __restrict__ offsets, int E, int pad,
+                                   int* __restrict__ tile_group, int n_tiles) {
   if (threadIdx.x == 0) {
-    int a = 0;
+    int a = 0, t = 0;
     for (int e = 0; e < E; e++) {
       offsets[e] = a;
-      a += counts[e];
+      a += (counts[e] + pad - 1) / pad * pad;
       counts[e] = 0;                              // reused as the fill counters of the placing pass
+      if (tile_group)
+        for (; t < n_tiles && t * pad < a; t++) tile_group[t] = e;
     }
     offsets[E] = a;
+    if (tile_group)
+      for (; t < n_tiles; t++) tile_group[t] = E - 1;
   }
 }
 __global__ void moe_place_kernel(const int* __restrict__ idx, int n_pairs, const int* __restrict__ offsets,
-                                 int* __restrict__ fill, int* __restrict__ pair_of_row) {
+                                 int* __restrict__ fill, int* __restrict__ pair_of_row, int* __restrict__ row_of_pair) {
   int p = blockIdx.x * blockDim.x + threadIdx.x;
   if (p >= n_pairs) return;
   int e = idx[p];
-  pair_of_row[offsets[e] + atomicAdd(&fill[e], 1)] = p;
+  int row = offsets[e] + atomicAdd(&fill[e], 1);
+  pair_of_row[row] = p;
+  if (row_of_pair) row_of_pair[p] = row;
+}
+
+// The grouped rows' inputs side by side: xs[row] = h[pair_of_row[row] / top], zeros for a row that holds no pair.
+template <typename A>
+__global__ void moe_gather_rows_kernel(const A* __restrict__ h, int ldh, const int* __restrict__ pair_of_row, int top,
+                                       A* __restrict__ xs, int K, int vec) {
+  int row = blockIdx.x;
+  int p = pair_of_row[row];
+  A* dst = xs + (size_t)row * K;
+  if (vec) {                                      // 16 bytes a thread: K * sizeof(A), ldh * sizeof(A) and both starts are multiples
+    constexpr int PER = 16 / sizeof(A);
+    const uint4 zero = make_uint4(0, 0, 0, 0);
+    for (int j = threadIdx.x * PER; j < K; j += blockDim.x * PER)
+      *(uint4*)(dst + j) = p >= 0 ? *(const uint4*)(h + (size_t)(p / top) * ldh + j) : zero;
+    return;
+  }
+  for (int j = threadIdx.x; j < K; j += blockDim.x) dst[j] = p >= 0 ? h[(size_t)(p / top) * ldh + j] : from_f32<A>(0.f);
+}
+
+// out[t] = sum_k wgt[t][k] * ys[row_of_pair[t * top + k]], the choices in their order: float32 [T, N].
+__global__ void moe_combine_kernel(const float* __restrict__ ys, const int* __restrict__ row_of_pair,
+                                   const float* __restrict__ wgt, float* __restrict__ out, int top, int N) {
+  int t = blockIdx.x;
+  for (int j = threadIdx.x; j < N; j += blockDim.x) {
+    float a = 0.f;
+    for (int k = 0; k < top; k++) a += wgt[(size_t)t * top + k] * ys[(size_t)row_of_pair[(size_t)t * top + k] * N + j];
+    out[(size_t)t * N + j] = a;
+  }
 }
 
 // The experts' products over the grouped rows: tiles of 64 rows x 64 columns of one expert, 16 of K at a time

@@ -13,10 +13,12 @@ of the chosen experts' outputs.
 
 The experts' matrices are stacked [experts, ff, hidden] and [experts, hidden, ff]. A step of few
 rows runs every (token, chosen expert) pair by itself (each streams its expert's matrices once); a
-longer step groups the pairs by expert on the device and runs tiles of rows per expert. Both
-launch the same work whatever the router chose, so a decode step can be captured. The weighted
-outputs leave as float32 partial sums [top, T, hidden], one per choice, which the next reader of
-the residual stream adds in a fixed order.
+longer step groups the pairs by expert on the device and runs tiles of rows per expert: in bfloat16
+on the tensor cores (every expert's rows start at a multiple of 128, the product kernel looks up
+each tile's expert, the weighted sum over a token's choices is a pass of its own), else on the FMA
+units. All launch the same work whatever the router chose, so a decode step can be captured. The
+weighted outputs leave as float32: partial sums [top, T, hidden], one per choice, which the next
+reader of the residual stream adds in a fixed order, or the sum itself.
 """
 from __future__ import annotations
 
@@ -90,20 +92,48 @@ class RoutedExperts(FeedForward):
         if self.router.dtype != dtype or self.w_up.dtype != dtype:
             raise ValueError(f"the experts' matrices are {self.w_up.dtype}, the engine runs in {dtype}")
 
+    def _on_tensor_cores(self, x) -> bool:
+        """The grouped products can run on the tensor-core kernel: bfloat16, and the contraction widths (hidden for the
+        experts' first product, their own width for the second) multiples of 8 elements (16 bytes for its copies)."""
+        return x.dtype == torch.bfloat16 and self.hidden % 8 == 0 and self.F % 8 == 0 and x.data_ptr() % 16 == 0
+
     def forward(self, x, ctx):
         k = ctx.kernels.mix
         T, dev = x.shape[0], x.device
+        pairs = T * self.top
         idx = torch.empty((T, self.top), dtype=torch.int32, device=dev)
         wgt = torch.empty((T, self.top), dtype=torch.float32, device=dev)
         k.moe_route(x, self.router, self.correction, idx, wgt, self.n_groups, self.keep, self.top, self.scale)
-        hid = torch.empty((T * self.top, self.F), dtype=x.dtype, device=dev)
-        out = torch.empty((self.top, T, self.hidden), dtype=torch.float32, device=dev)
-        if T * self.top <= self.PAIRS_ONE_BY_ONE:
+        if pairs <= self.PAIRS_ONE_BY_ONE:
+            hid = torch.empty((pairs, self.F), dtype=x.dtype, device=dev)
+            out = torch.empty((self.top, T, self.hidden), dtype=torch.float32, device=dev)
             k.moe_pairs(x, self.w_up, self.w_down, idx, wgt, hid, out)
-        else:
-            offsets = torch.empty((self.E + 1,), dtype=torch.int32, device=dev)
-            pair_of_row = torch.empty((T * self.top,), dtype=torch.int32, device=dev)
-            k.moe_grouped(x, self.w_up, self.w_down, idx, wgt, self.counts, offsets, pair_of_row, hid, out)
+            return out
+        offsets = torch.empty((self.E + 1,), dtype=torch.int32, device=dev)
+        if not self._on_tensor_cores(x):
+            pair_of_row = torch.empty((pairs,), dtype=torch.int32, device=dev)
+            k.moe_group_rows(idx, self.counts, offsets, pair_of_row)
+            hid = torch.empty((pairs, self.F), dtype=x.dtype, device=dev)
+            out = torch.empty((self.top, T, self.hidden), dtype=torch.float32, device=dev)
+            k.moe_grouped(x, self.w_up, self.w_down, wgt, offsets, pair_of_row, hid, out)
+            return out
+        # every expert's rows from a multiple of 128 on, so that a tile of the tensor-core product has one expert
+        tile = 128
+        rows = -(-(pairs + self.E * (tile - 1)) // tile) * tile
+        pair_of_row = torch.empty((rows,), dtype=torch.int32, device=dev)
+        row_of_pair = torch.empty((pairs,), dtype=torch.int32, device=dev)
+        tile_group = torch.empty((rows // tile,), dtype=torch.int32, device=dev)
+        k.moe_group_rows(idx, self.counts, offsets, pair_of_row, row_of_pair, tile_group, pad=tile)
+        xs = torch.empty((rows, self.hidden), dtype=x.dtype, device=dev)
+        k.moe_gather_rows(x, pair_of_row, self.top, xs)
+        tc = ctx.kernels.tensor_core
+        hid = torch.empty((rows, self.F), dtype=x.dtype, device=dev)
+        tc.gemm_grouped(xs, self.w_up, hid, tile_group, ctx.err_flag)
+        k.act_inplace(hid, "relu_squared")
+        ys = torch.empty((rows, self.hidden), dtype=torch.float32, device=dev)
+        tc.gemm_grouped(hid, self.w_down, ys, tile_group, ctx.err_flag)
+        out = torch.empty((T, self.hidden), dtype=torch.float32, device=dev)
+        k.moe_combine(ys, row_of_pair, wgt, out)
         return out
 
 
