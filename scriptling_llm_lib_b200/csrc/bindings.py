@@ -796,6 +796,23 @@ class MixKernels:
             _ptr(pages, self.dtype if pages is not None else None, "pages"), c_int(q.shape[0]), c_int(rank), c_int(rot_dim),
             _stream()), "latent_store")
 
+    def latent_gather(self, pages, ctx, block_table, dense):
+        """dense[t] = the cached vector at row t's (sequence, position)."""
+        _check(self._fn("latent_gather")(_ptr(pages, self.dtype, "pages"), _ptr(ctx.tok_pos, torch.int32, "tok_pos"),
+                                         _ptr(ctx.tok_seq, torch.int32, "tok_seq"), _ptr(block_table, torch.int32, "block_table"),
+                                         c_int(block_table.shape[1]), _ptr(dense, self.dtype, "dense"), c_int(dense.shape[0]),
+                                         c_int(dense.shape[1]), _stream()), "latent_gather")
+
+    def latent_heads(self, q, kv, dense, rank, ctx, table, kt, vt, qt, n_heads, dim, rot_dim, v_dim, hd):
+        """Keys [Wuk c | rotated part | 0], values [Wuv c | 0] and queries [q | 0] per head, `hd` wide, keys and values
+        into pages of their own by `table` (a prompt step from position 0)."""
+        _check(self._fn("latent_heads")(self._view(q, "q"), c_int(q.stride(0)), self._view(kv, "kv"), c_int(kv.stride(0)),
+                                        self._view(dense, "dense"), c_int(dense.stride(0)), c_int(rank),
+                                        _ptr(ctx.tok_pos, torch.int32, "tok_pos"), _ptr(ctx.tok_seq, torch.int32, "tok_seq"),
+                                        _ptr(table, torch.int32, "table"), c_int(table.shape[1]), _ptr(kt, self.dtype, "kt"),
+                                        _ptr(vt, self.dtype, "vt"), _ptr(qt, self.dtype, "qt"), c_int(q.shape[0]), c_int(n_heads),
+                                        c_int(dim), c_int(rot_dim), c_int(v_dim), c_int(hd), _stream()), "latent_heads")
+
     def latent_absorb(self, q, wuk, qa, n_heads, dim, rot_dim, rank, scale):
         """qa float32 [T, H, rank + rot_dim] = scale * [Wuk_h^T q_h[:dim] | q_h[dim:]] for every head."""
         if q.dtype != self.dtype:
@@ -811,10 +828,13 @@ class MixKernels:
             _ptr(part, torch.float32, "part"), c_int(qa.shape[0]), c_int(n_heads), c_int(rank), c_int(rot_dim), c_int(n_split),
             _stream()), "latent_attn")
 
-    def latent_expand(self, part, wuv, out, n_heads, v_dim, rank, n_split):
-        _check(self._fn("latent_expand")(_ptr(part, torch.float32, "part"), _ptr(wuv, self.dtype, "wuv"), _ptr(out, self.dtype, "out"),
-                                         c_int(out.shape[1]), c_int(out.shape[0]), c_int(n_heads), c_int(v_dim), c_int(rank),
-                                         c_int(n_split), _stream()), "latent_expand")
+    def latent_expand(self, part, olat, wuv, out, n_heads, v_dim, rank, n_split):
+        """Merges the splits of `part` into olat float32 [T, H, rank] (scratch), then out[t, h] = Wuv_h olat[t, h]."""
+        _check(self._fn("latent_expand")(_ptr(part, torch.float32, "part"), _ptr(olat, torch.float32, "olat"),
+                                         _ptr(wuv, self.dtype, "wuv"), _ptr(out, self.dtype, "out"), c_int(out.shape[1]),
+                                         c_int(out.shape[0]), c_int(n_heads), c_int(v_dim), c_int(rank), c_int(n_split), _stream()),
+               "latent_expand")
+        LAUNCHES[0] += 1
 
     def selective_scan(self, x, dt_raw, dt_bias, a_log, dskip, bc, b_col, c_col, z, state, ctx, out, inner, n_state):
         """x, z [T, I] views and bc [T, ...] of the element type (B at b_col, C at c_col), dt_raw float32 [T, I],
@@ -832,12 +852,12 @@ class MixKernels:
             _ptr(ctx.slots, torch.int32, "slots"), self._view(out, "out"), c_int(out.stride(0)), c_int(ctx.n_seqs), c_int(inner),
             c_int(n_state), _stream()), "selective_scan")
 
-    def moe_route(self, h, wr, correction, idx, wgt, n_groups, keep, top, scale):
-        T, K = h.shape
-        _check(self._fn("moe_route")(self._view(h, "h"), c_int(h.stride(0)), _ptr(wr, self.dtype, "router"),
-                                     _ptr(correction, torch.float32, "correction"), c_int(1), _ptr(idx, torch.int32, "idx"),
-                                     _ptr(wgt, torch.float32, "wgt"), c_int(T), c_int(K), c_int(wr.shape[0]), c_int(n_groups),
-                                     c_int(keep), c_int(top), c_float(scale), _stream()), "moe_route")
+    def moe_route(self, z, correction, idx, wgt, n_groups, keep, top, scale):
+        """z float32 [T, E] the router's logits -> idx int32 [T, top] the chosen experts, wgt float32 [T, top] their weights."""
+        T, E = z.shape
+        _check(self._fn("moe_route")(_ptr(z, torch.float32, "z"), _ptr(correction, torch.float32, "correction"), c_int(1),
+                                     _ptr(idx, torch.int32, "idx"), _ptr(wgt, torch.float32, "wgt"), c_int(T), c_int(E),
+                                     c_int(n_groups), c_int(keep), c_int(top), c_float(scale), _stream()), "moe_route")
 
     def moe_pairs(self, h, wup, wdown, idx, wgt, hid, out):
         """wup [E, F, K], wdown [E, N, F]; out float32 [top, T, N] partial sums over a token's chosen experts."""

@@ -294,6 +294,37 @@ __global__ void latent_store_kernel(A* __restrict__ q, int ldq, int H, int D, co
   }
 }
 
+// gather: the cached vectors of a step's rows side by side, dense[t] = pages[place of (sequence, position) of row t].
+template <typename A>
+__global__ void latent_gather_kernel(const A* __restrict__ pages, const int* __restrict__ tok_pos, const int* __restrict__ tok_seq,
+                                     const int* __restrict__ block_table, int max_pages, A* __restrict__ dense, int W) {
+  int t = blockIdx.x;
+  int pos = tok_pos[t];
+  const A* src = pages + ((size_t)block_table[(size_t)tok_seq[t] * max_pages + pos / SLLM_PAGE] * SLLM_PAGE + pos % SLLM_PAGE) * W;
+  for (int j = threadIdx.x; j < W; j += blockDim.x) dense[(size_t)t * W + j] = src[j];
+}
+
+// heads: keys and values per head for a prompt that starts at position 0, laid out as pages of their own so that an
+// attention kernel for keys and values of one width `hd` >= max(D + P, V) can run on them. kv[t] = [Wuk c | Wuv c] (H D
+// and H V wide), dense[t][R ..] the rotated key part. kt[page][h][place] = [key of head h | rotated part | 0 ..],
+// vt[...] = [value of head h | 0 ..], qt[t][h] = [query of head h (D + P) | 0 ..]; the page of (sequence, position) comes
+// from `table` [sequences][max_pages].
+template <typename A>
+__global__ void latent_heads_kernel(const A* __restrict__ q, int ldq, const A* __restrict__ kv, int ldkv,
+                                    const A* __restrict__ dense, int ldd, int R, const int* __restrict__ tok_pos,
+                                    const int* __restrict__ tok_seq, const int* __restrict__ table, int max_pages,
+                                    A* __restrict__ kt, A* __restrict__ vt, A* __restrict__ qt, int H, int D, int P, int V, int hd) {
+  int t = blockIdx.x, h = blockIdx.y;
+  int pos = tok_pos[t];
+  size_t at = (((size_t)table[(size_t)tok_seq[t] * max_pages + pos / SLLM_PAGE] * H + h) * SLLM_PAGE + pos % SLLM_PAGE) * hd;
+  const A zero = from_f32<A>(0.f);
+  for (int j = threadIdx.x; j < hd; j += blockDim.x) {
+    kt[at + j] = j < D ? kv[(size_t)t * ldkv + (size_t)h * D + j] : (j < D + P ? dense[(size_t)t * ldd + R + j - D] : zero);
+    vt[at + j] = j < V ? kv[(size_t)t * ldkv + (size_t)H * D + (size_t)h * V + j] : zero;
+    qt[((size_t)t * H + h) * hd + j] = j < D + P ? q[(size_t)t * ldq + (size_t)h * (D + P) + j] : zero;
+  }
+}
+
 // absorb: the query a head asks the latent with. qa[t][h] = scale * [ Wuk_h^T q_unrot | q_rot ] (float32, R + P
 // wide), Wuk_h = rows h D .. h D + D - 1 of the stored [H D, R] matrix. A block takes up to 8 rows of one head;
 // threads run over the latent's columns, so a row of the matrix is read in one piece.
@@ -311,10 +342,12 @@ __global__ void __launch_bounds__(128) latent_absorb_kernel(const A* __restrict_
   }
   __syncthreads();
   const A* w = wuk + (size_t)h * D * R;
-  for (int c = threadIdx.x; c < R; c += blockDim.x) {
+  int c = blockIdx.z * blockDim.x + threadIdx.x;  // a latent column a thread
+  if (c < R) {
     float acc[MIX_ABSORB_ROWS];
 #pragma unroll
     for (int r = 0; r < MIX_ABSORB_ROWS; r++) acc[r] = 0.f;
+#pragma unroll 8
     for (int d = 0; d < D; d++) {
       float wv = to_f32(w[(size_t)d * R + c]);
 #pragma unroll
@@ -322,10 +355,11 @@ __global__ void __launch_bounds__(128) latent_absorb_kernel(const A* __restrict_
     }
     for (int r = 0; r < n; r++) qa[((size_t)(t0 + r) * H + h) * (R + P) + c] = acc[r];
   }
-  for (int i = threadIdx.x; i < n * P; i += blockDim.x) {
-    int r = i / P, j = i % P;
-    qa[((size_t)(t0 + r) * H + h) * (R + P) + R + j] = to_f32(q[(size_t)(t0 + r) * ldq + (size_t)h * (D + P) + D + j]) * scale;
-  }
+  if (blockIdx.z == 0)
+    for (int i = threadIdx.x; i < n * P; i += blockDim.x) {
+      int r = i / P, j = i % P;
+      qa[((size_t)(t0 + r) * H + h) * (R + P) + R + j] = to_f32(q[(size_t)(t0 + r) * ldq + (size_t)h * (D + P) + D + j]) * scale;
+    }
 }
 
 // scores and sums: one block per (row, group of up to 8 heads, split of the keys), a warp per head. Keys arrive in
@@ -337,7 +371,7 @@ template <typename A, int NV>
 __global__ void __launch_bounds__(256) latent_attn_kernel(const float* __restrict__ qa, const A* __restrict__ pages,
                                                           const int* __restrict__ tok_pos, const int* __restrict__ tok_seq,
                                                           const int* __restrict__ block_table, int max_pages,
-                                                          float* __restrict__ part, int H, int R, int P, int n_split) {
+                                                          float* __restrict__ part, int H, int R, int P, int n_split, int vec) {
   extern __shared__ __align__(16) float sm[];
   int W = R + P, Wp = W + 1;
   int t = blockIdx.x, h0 = blockIdx.y * 8, sp = blockIdx.z;
@@ -361,14 +395,33 @@ __global__ void __launch_bounds__(256) latent_attn_kernel(const float* __restric
     int k0 = tile * 32;
     int nk = min(32, pos + 1 - k0);
     __syncthreads();
-    for (int i = threadIdx.x; i < 32 * W; i += nthreads) {
-      int kr = i / W, d = i % W;
-      float v = 0.f;
-      if (kr < nk) {
-        int kp = k0 + kr;
-        v = to_f32(pages[((size_t)pt[kp / SLLM_PAGE] * SLLM_PAGE + kp % SLLM_PAGE) * W + d]);
+    // a tile of 32 keys lies inside one page (32 divides the page size): one look-up for the tile, then whole rows a warp
+    const A* tile_src = pages + ((size_t)pt[k0 / SLLM_PAGE] * SLLM_PAGE + k0 % SLLM_PAGE) * W;
+    constexpr int VEC = 16 / sizeof(A);
+    if (vec) {
+      int chunks = W / VEC;
+      for (int i = threadIdx.x; i < 32 * chunks; i += nthreads) {
+        int kr = i / chunks, d = (i % chunks) * VEC;
+        float* dst = Ks + kr * Wp + d;
+        if (kr < nk) {
+          if constexpr (sizeof(A) == 2) {
+            F8 f = ld8((const bf16*)(tile_src + (size_t)kr * W + d));
+#pragma unroll
+            for (int e = 0; e < 8; e++) dst[e] = f.f[e];
+          } else {
+            float4 f = *(const float4*)(tile_src + (size_t)kr * W + d);
+            dst[0] = f.x; dst[1] = f.y; dst[2] = f.z; dst[3] = f.w;
+          }
+        } else {
+#pragma unroll
+          for (int e = 0; e < VEC; e++) dst[e] = 0.f;
+        }
       }
-      Ks[kr * Wp + d] = v;
+    } else {
+      for (int i = threadIdx.x; i < 32 * W; i += nthreads) {
+        int kr = i / W, d = i % W;
+        Ks[kr * Wp + d] = kr < nk ? to_f32(tile_src[(size_t)kr * W + d]) : 0.f;
+      }
     }
     __syncthreads();
     if (!active) continue;
@@ -408,63 +461,67 @@ __global__ void __launch_bounds__(256) latent_attn_kernel(const float* __restric
   }
 }
 
-// expand: merges the splits' sums over the latent and maps them to the head's values: out[t][h V + v] =
-// Wuv[h V + v] . (sum_s w_s acc_s / sum_s w_s l_s), w_s = exp(m_s - max m). A block takes up to 8 rows of one head,
-// a warp an output column at a time.
+// merge: olat[t][h] = sum_s w_s acc_s / sum_s w_s l_s, w_s = exp(m_s - max m): the splits' sums over the latent as one
+// normalised vector [R] per (row, head).
+__global__ void latent_merge_kernel(const float* __restrict__ part, float* __restrict__ olat, int R, int n_split) {
+  size_t item = blockIdx.x;                       // t * H + h
+  const float* p0 = part + item * n_split * (R + 2);
+  float mx = -INFINITY;
+  for (int s = 0; s < n_split; s++) mx = fmaxf(mx, p0[(size_t)s * (R + 2)]);
+  float den = 0.f;
+  for (int s = 0; s < n_split; s++) {
+    float ms = p0[(size_t)s * (R + 2)];
+    if (ms > -INFINITY) den += expf(ms - mx) * p0[(size_t)s * (R + 2) + 1];
+  }
+  float inv = 1.0f / den;
+  for (int c = threadIdx.x; c < R; c += blockDim.x) {
+    float a = 0.f;
+    for (int s = 0; s < n_split; s++) {
+      float ms = p0[(size_t)s * (R + 2)];
+      if (ms > -INFINITY) a += expf(ms - mx) * p0[(size_t)s * (R + 2) + 2 + c];
+    }
+    olat[item * R + c] = a * inv;
+  }
+}
+
+// expand: maps the summed latents to the head's values: out[t][h V + v] = Wuv[h V + v] . olat[t][h]. A block takes up
+// to 8 rows of one head and four output columns, a warp a column.
 template <typename A>
-__global__ void __launch_bounds__(128) latent_expand_kernel(const float* __restrict__ part, const A* __restrict__ wuv,
-                                                            A* __restrict__ out, int ldo, int T, int H, int V, int R,
-                                                            int n_split) {
+__global__ void __launch_bounds__(128) latent_expand_kernel(const float* __restrict__ olat, const A* __restrict__ wuv,
+                                                            A* __restrict__ out, int ldo, int T, int H, int V, int R) {
   extern __shared__ __align__(16) float sm[];     // [8][R]
   int h = blockIdx.y, t0 = blockIdx.x * MIX_ABSORB_ROWS;
   int n = min(MIX_ABSORB_ROWS, T - t0);
-  int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
-  for (int r = 0; r < MIX_ABSORB_ROWS; r++) {
-    if (r >= n) {
-      for (int c = threadIdx.x; c < R; c += blockDim.x) sm[r * R + c] = 0.f;
-      continue;
-    }
-    const float* p0 = part + ((size_t)(t0 + r) * H + h) * n_split * (R + 2);
-    float mx = -INFINITY;
-    for (int s = 0; s < n_split; s++) mx = fmaxf(mx, p0[(size_t)s * (R + 2)]);
-    float den = 0.f;
-    for (int s = 0; s < n_split; s++) {
-      float ms = p0[(size_t)s * (R + 2)];
-      if (ms > -INFINITY) den += expf(ms - mx) * p0[(size_t)s * (R + 2) + 1];
-    }
-    float inv = 1.0f / den;
-    for (int c = threadIdx.x; c < R; c += blockDim.x) {
-      float a = 0.f;
-      for (int s = 0; s < n_split; s++) {
-        float ms = p0[(size_t)s * (R + 2)];
-        if (ms > -INFINITY) a += expf(ms - mx) * p0[(size_t)s * (R + 2) + 2 + c];
-      }
-      sm[r * R + c] = a * inv;
-    }
+  int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  for (int i = threadIdx.x; i < MIX_ABSORB_ROWS * R; i += blockDim.x) {
+    int r = i / R, c = i % R;
+    sm[i] = r < n ? olat[((size_t)(t0 + r) * H + h) * R + c] : 0.f;
   }
   __syncthreads();
-  for (int v = wid; v < V; v += nw) {
-    const A* w = wuv + ((size_t)h * V + v) * R;
-    float acc[MIX_ABSORB_ROWS];
+  int v = blockIdx.z * 4 + wid;
+  if (v >= V) return;
+  const A* w = wuv + ((size_t)h * V + v) * R;
+  float acc[MIX_ABSORB_ROWS];
 #pragma unroll
-    for (int r = 0; r < MIX_ABSORB_ROWS; r++) acc[r] = 0.f;
-    for (int c = lane; c < R; c += 32) {
-      float wv = to_f32(w[c]);
+  for (int r = 0; r < MIX_ABSORB_ROWS; r++) acc[r] = 0.f;
+#pragma unroll 4
+  for (int c = lane; c < R; c += 32) {
+    float wv = to_f32(w[c]);
 #pragma unroll
-      for (int r = 0; r < MIX_ABSORB_ROWS; r++) acc[r] += sm[r * R + c] * wv;
-    }
-#pragma unroll
-    for (int r = 0; r < MIX_ABSORB_ROWS; r++) acc[r] = warp_sum(acc[r]);
-    if (lane == 0)
-      for (int r = 0; r < n; r++) out[(size_t)(t0 + r) * ldo + (size_t)h * V + v] = from_f32<A>(acc[r]);
+    for (int r = 0; r < MIX_ABSORB_ROWS; r++) acc[r] += sm[r * R + c] * wv;
   }
+#pragma unroll
+  for (int r = 0; r < MIX_ABSORB_ROWS; r++) acc[r] = warp_sum(acc[r]);
+  if (lane == 0)
+    for (int r = 0; r < n; r++) out[(size_t)(t0 + r) * ldo + (size_t)h * V + v] = from_f32<A>(acc[r]);
 }
 
 // ------------------------------------------------------------------ the selective scan
 // Per channel c a state S[c][0..N): for each row dt = softplus(dt_raw[c] + dt_bias[c]);
 // S[c][n] <- exp(dt * A[c][n]) * S[c][n] + dt * x[c] * B[n];  y[c] = sum_n S[c][n] * C[n] + D[c] * x[c];  out = y * silu(z[c]),
 // A = -exp(A_log). Four lanes share a channel (every fourth state each); a block takes 32 channels of one sequence and
-// walks its rows. x, z, B, C: column slices of buffers of the element type; dt_raw float32.
+// walks its rows, which a second set of warps stages in shared memory ahead of the walk. x, z, B, C: column slices of
+// buffers of the element type; dt_raw float32.
 struct ScanArgs {
   const void* x; int ldx;
   const float* dt_raw; int lddt;
@@ -477,86 +534,133 @@ struct ScanArgs {
   int I, N;
 };
 
+#define MIX_SCAN_ROWS 16      // rows staged at a time
 template <typename A, int NPL>
-__global__ void __launch_bounds__(128) selective_scan_kernel(ScanArgs p) {
-  int b = blockIdx.y;
-  int ch = blockIdx.x * 32 + (threadIdx.x >> 2), l = threadIdx.x & 3;
-  bool live = ch < p.I;
-  int c = live ? ch : p.I - 1;
-  float Areg[NPL], S[NPL];
-  float* st = p.state + ((size_t)p.slots[b] * p.I + c) * p.N;
-#pragma unroll
-  for (int i = 0; i < NPL; i++) {
-    int n = l + 4 * i;
-    Areg[i] = n < p.N ? -expf(load_w(p.a_log, p.w_f32, (size_t)c * p.N + n)) : 0.f;
-    S[i] = n < p.N ? st[n] : 0.f;
-  }
-  float bias = load_w(p.dt_bias, p.w_f32, c), dsk = load_w(p.dskip, p.w_f32, c);
+__global__ void __launch_bounds__(256) selective_scan_kernel(ScanArgs p) {
+  // Warps 0-3 walk the rows (32 channels x 4 lanes); warps 4-7 stage the next MIX_SCAN_ROWS rows meanwhile: step sizes with
+  // their softplus, inputs, gates with their SiLU (32 channels a row) and the rows' B and C (N each), two buffers in turn.
+  extern __shared__ __align__(16) float sm[];
+  const int N = p.N, per_buf = MIX_SCAN_ROWS * (96 + 2 * N);
+  int b = blockIdx.y, ch0 = blockIdx.x * 32;
+  int r_begin = p.seq_start[b], r_end = p.seq_start[b + 1];
+  int n_chunks = (r_end - r_begin + MIX_SCAN_ROWS - 1) / MIX_SCAN_ROWS;
   const A* xs = (const A*)p.x;
   const A* zs = (const A*)p.z;
   const A* bcs = (const A*)p.bc;
   A* out = (A*)p.out;
-  int r_end = p.seq_start[b + 1];
-  for (int r = p.seq_start[b]; r < r_end; r++) {
-    float dt = softplus_f(p.dt_raw[(size_t)r * p.lddt + c] + bias);
-    float xv = to_f32(xs[(size_t)r * p.ldx + c]);
-    float dx = dt * xv;
-    const A* brow = bcs + (size_t)r * p.ldbc;
-    float acc = 0.f;
+  bool loader = threadIdx.x >= 128;
+  int lt = threadIdx.x - 128;
+
+  auto stage = [&](int chunk) {
+    float* buf = sm + (size_t)(chunk & 1) * per_buf;
+    float *dt_s = buf, *x_s = buf + MIX_SCAN_ROWS * 32, *z_s = x_s + MIX_SCAN_ROWS * 32, *b_s = z_s + MIX_SCAN_ROWS * 32,
+          *c_s = b_s + MIX_SCAN_ROWS * N;
+    int r0 = r_begin + chunk * MIX_SCAN_ROWS;
+    int n = min(MIX_SCAN_ROWS, r_end - r0);
+    for (int i = lt; i < MIX_SCAN_ROWS * 32; i += 128) {
+      int r = i >> 5, ch = ch0 + (i & 31);
+      float dt = 0.f, xv = 0.f, zv = 0.f;
+      if (r < n && ch < p.I) {
+        dt = softplus_f(p.dt_raw[(size_t)(r0 + r) * p.lddt + ch] + load_w(p.dt_bias, p.w_f32, ch));
+        xv = to_f32(xs[(size_t)(r0 + r) * p.ldx + ch]);
+        zv = silu_f(to_f32(zs[(size_t)(r0 + r) * p.ldz + ch]));
+      }
+      dt_s[i] = dt; x_s[i] = xv; z_s[i] = zv;
+    }
+    for (int i = lt; i < MIX_SCAN_ROWS * N; i += 128) {
+      int r = i / N, nn = i % N;
+      float bv = 0.f, cv = 0.f;
+      if (r < n) {
+        const A* row = bcs + (size_t)(r0 + r) * p.ldbc;
+        bv = to_f32(row[p.b_col + nn]);
+        cv = to_f32(row[p.c_col + nn]);
+      }
+      b_s[i] = bv; c_s[i] = cv;
+    }
+  };
+
+  int cc = (threadIdx.x & 127) >> 2, l = threadIdx.x & 3;
+  int ch = ch0 + cc;
+  bool live = !loader && ch < p.I;
+  int c = min(ch, p.I - 1);
+  float Areg[NPL], S[NPL];
+  float* st = p.state + ((size_t)p.slots[b] * p.I + c) * N;
+  float dsk = 0.f;
+  if (!loader) {
 #pragma unroll
     for (int i = 0; i < NPL; i++) {
       int n = l + 4 * i;
-      if (n < p.N) {
-        S[i] = expf(dt * Areg[i]) * S[i] + dx * to_f32(brow[p.b_col + n]);
-        acc += S[i] * to_f32(brow[p.c_col + n]);
+      Areg[i] = n < N ? -expf(load_w(p.a_log, p.w_f32, (size_t)c * N + n)) : 0.f;
+      S[i] = n < N ? st[n] : 0.f;
+    }
+    dsk = load_w(p.dskip, p.w_f32, c);
+  } else if (n_chunks > 0) {
+    stage(0);
+  }
+  __syncthreads();
+  for (int chunk = 0; chunk < n_chunks; chunk++) {
+    if (loader) {
+      if (chunk + 1 < n_chunks) stage(chunk + 1);
+    } else {
+      const float* buf = sm + (size_t)(chunk & 1) * per_buf;
+      const float *dt_s = buf, *x_s = buf + MIX_SCAN_ROWS * 32, *z_s = x_s + MIX_SCAN_ROWS * 32, *b_s = z_s + MIX_SCAN_ROWS * 32,
+                  *c_s = b_s + MIX_SCAN_ROWS * N;
+      int r0 = r_begin + chunk * MIX_SCAN_ROWS;
+      int n = min(MIX_SCAN_ROWS, r_end - r0);
+      for (int r = 0; r < n; r++) {
+        float dt = dt_s[r * 32 + cc], xv = x_s[r * 32 + cc];
+        float dx = dt * xv;
+        const float* brow = b_s + r * N;
+        const float* crow = c_s + r * N;
+        float acc = 0.f;
+#pragma unroll
+        for (int i = 0; i < NPL; i++) {
+          int nn = l + 4 * i;
+          if (nn < N) {
+            S[i] = expf(dt * Areg[i]) * S[i] + dx * brow[nn];
+            acc += S[i] * crow[nn];
+          }
+        }
+        acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+        acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+        if (l == 0 && live) out[(size_t)(r0 + r) * p.ldo + ch] = from_f32<A>((acc + dsk * xv) * z_s[r * 32 + cc]);
       }
     }
-    acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-    acc += __shfl_xor_sync(0xffffffffu, acc, 2);
-    if (l == 0 && live) {
-      float y = acc + dsk * xv;
-      out[(size_t)r * p.ldo + c] = from_f32<A>(y * silu_f(to_f32(zs[(size_t)r * p.ldz + c])));
-    }
+    __syncthreads();
   }
   if (live) {
 #pragma unroll
     for (int i = 0; i < NPL; i++) {
       int n = l + 4 * i;
-      if (n < p.N) st[n] = S[i];
+      if (n < N) st[n] = S[i];
     }
   }
 }
 
 // ------------------------------------------------------------------ routed experts
-// router: one block per token. z = Wr h (float32 sums), s = sigmoid(z), choice = s + correction. Experts form
-// n_groups equal groups of neighbours; a group's score is the sum of its two largest choices; only experts of the
-// `keep` best groups can be chosen; the `top` largest choices among them are taken (ties: the lower index). Their
-// weights are s / (sum of the chosen s + 1e-20) * scale. idx int32 [T][top], wgt float32 [T][top].
-template <typename A>
-__global__ void __launch_bounds__(128) moe_route_kernel(const A* __restrict__ h, int ldh, const A* __restrict__ wr,
-                                                        const void* __restrict__ corr, int corr_f32, int* __restrict__ idx,
-                                                        float* __restrict__ wgt, int K, int E, int n_groups, int keep, int top,
-                                                        float scale) {
+// router: a warp per token. z [T][E] float32 are the router's logits (a product of the library, float32 sums);
+// s = sigmoid(z), choice = s + correction. Experts form n_groups equal groups of neighbours; a group's score is the sum
+// of its two largest choices; only experts of the `keep` best groups can be chosen; the `top` largest choices among
+// them are taken (ties: the lower index). Their weights are s / (sum of the chosen s + 1e-20) * scale.
+// idx int32 [T][top], wgt float32 [T][top].
+#define MIX_ROUTE_WARPS 4
+__global__ void __launch_bounds__(32 * MIX_ROUTE_WARPS) moe_route_kernel(const float* __restrict__ z, const void* __restrict__ corr,
+                                                                         int corr_f32, int* __restrict__ idx,
+                                                                         float* __restrict__ wgt, int T, int E, int n_groups,
+                                                                         int keep, int top, float scale) {
   extern __shared__ __align__(16) float sm[];
-  float* s = sm;                    // [E] sigmoid scores
-  float* ch = s + E;                // [E] choice scores (minus infinity once taken or shut out)
-  float* gs = ch + E;               // [n_groups]
-  int t = blockIdx.x;
-  int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
-  const A* x = h + (size_t)t * ldh;
-  for (int e = wid; e < E; e += nw) {
-    const A* w = wr + (size_t)e * K;
-    float a = 0.f;
-    for (int k = lane; k < K; k += 32) a += to_f32(x[k]) * to_f32(w[k]);
-    a = warp_sum(a);
-    if (lane == 0) {
-      float sg = sigmoid_f(a);
-      s[e] = sg;
-      ch[e] = sg + load_w(corr, corr_f32, e);
-    }
+  int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  int t = blockIdx.x * MIX_ROUTE_WARPS + wid;
+  if (t >= T) return;
+  float* s = sm + (size_t)wid * (2 * E + n_groups);   // [E] sigmoid scores
+  float* ch = s + E;                                  // [E] choice scores (minus infinity once taken or shut out)
+  float* gs = ch + E;                                 // [n_groups]
+  for (int e = lane; e < E; e += 32) {
+    float sg = sigmoid_f(z[(size_t)t * E + e]);
+    s[e] = sg;
+    ch[e] = sg + load_w(corr, corr_f32, e);
   }
-  __syncthreads();
-  if (wid != 0) return;
+  __syncwarp();
   int gsz = E / n_groups;
   if (n_groups > 1) {
     for (int g = lane; g < n_groups; g += 32) {
@@ -620,33 +724,42 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const A* __restrict__ h,
 //   up:   hid[p][f] = relu(Wup[e_p][f] . h[t_p])^2           p = t * top + k
 //   down: out[k][t][j] = wgt[p] * (Wdown[e_p][j] . hid[p])    float32 partial sums over k, added by the reader
 template <typename A>
+__device__ __forceinline__ float warp_dot(const A* __restrict__ x, const A* __restrict__ w, int K, int lane, int vec) {
+  float a0 = 0.f, a1 = 0.f;
+  if (vec) {                                      // eight elements a lane and pass: K and both rows' starts are multiples of 8 elements
+#pragma unroll 2
+    for (int k = lane * 8; k < K; k += 256) {
+      F8 xv = ld8(x + k), wv = ld8(w + k);
+      a0 += xv.f[0] * wv.f[0] + xv.f[2] * wv.f[2] + xv.f[4] * wv.f[4] + xv.f[6] * wv.f[6];
+      a1 += xv.f[1] * wv.f[1] + xv.f[3] * wv.f[3] + xv.f[5] * wv.f[5] + xv.f[7] * wv.f[7];
+    }
+  } else {
+    for (int k = lane; k < K; k += 32) a0 += to_f32(x[k]) * to_f32(w[k]);
+  }
+  return warp_sum(a0 + a1);
+}
+
+template <typename A>
 __global__ void __launch_bounds__(128) moe_pair_up_kernel(const A* __restrict__ h, int ldh, const A* __restrict__ wup,
-                                                          const int* __restrict__ idx, A* __restrict__ hid, int top, int K, int F) {
+                                                          const int* __restrict__ idx, A* __restrict__ hid, int top, int K, int F,
+                                                          int vec) {
   int p = blockIdx.y;
   int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
   int f = blockIdx.x * nw + wid;
   if (f >= F) return;
-  const A* x = h + (size_t)(p / top) * ldh;
-  const A* w = wup + ((size_t)idx[p] * F + f) * K;
-  float a = 0.f;
-  for (int k = lane; k < K; k += 32) a += to_f32(x[k]) * to_f32(w[k]);
-  a = warp_sum(a);
+  float a = warp_dot(h + (size_t)(p / top) * ldh, wup + ((size_t)idx[p] * F + f) * K, K, lane, vec);
   if (lane == 0) hid[(size_t)p * F + f] = from_f32<A>(a > 0.f ? a * a : 0.f);
 }
 
 template <typename A>
 __global__ void __launch_bounds__(128) moe_pair_down_kernel(const A* __restrict__ hid, const A* __restrict__ wdown,
                                                             const int* __restrict__ idx, const float* __restrict__ wgt,
-                                                            float* __restrict__ out, int T, int top, int F, int N) {
+                                                            float* __restrict__ out, int T, int top, int F, int N, int vec) {
   int p = blockIdx.y;
   int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
   int j = blockIdx.x * nw + wid;
   if (j >= N) return;
-  const A* x = hid + (size_t)p * F;
-  const A* w = wdown + ((size_t)idx[p] * N + j) * F;
-  float a = 0.f;
-  for (int k = lane; k < F; k += 32) a += to_f32(x[k]) * to_f32(w[k]);
-  a = warp_sum(a);
+  float a = warp_dot(hid + (size_t)p * F, wdown + ((size_t)idx[p] * N + j) * F, F, lane, vec);
   if (lane == 0) out[((size_t)(p % top) * T + p / top) * N + j] = wgt[p] * a;
 }
 

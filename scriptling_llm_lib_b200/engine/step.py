@@ -85,6 +85,9 @@ class StepContext:
         self.token_ids = self.tok_pos = self.tok_seq = self.seq_start = self.seq_pos0 = self.slots = None
         self.seq_pos_after = None
         self.block_tables: list[torch.Tensor] = []
+        self.seq_lens_host: list[int] | None = None     # rows of every sequence, known on the host (None in a replayed step)
+        self.from_start = False                         # every sequence of the step starts at its position 0
+        self.scratch: dict = {}                         # what parts of one kind share within a step (made by the first to ask)
 
     @property
     def kernels_f32(self):
@@ -412,6 +415,8 @@ class Engine:
         ctx.token_ids, ctx.tok_pos, ctx.tok_seq, ctx.seq_start, ctx.seq_pos0, ctx.slots, ctx.want_rows, ctx.seq_pos_after = views[:8]
         ctx.block_tables = [v.view(B, t.shape[1]) for v, t in zip(views[8:], tables)]
         ctx.is_decode = bool((lens_a == 1).all())
+        ctx.seq_lens_host = [int(n) for n in lens]
+        ctx.from_start = not pos0_a.any()
         ctx.max_pages = int(-(-(int((pos0_a + lens_a).max())) // PAGE))
         ctx._host_keepalive = host
         return ctx

@@ -4,7 +4,7 @@
 square of relu, or silu.
 
 `routed_experts`: `experts` such feed-forwards (act = relu^2 by default) of which every token uses
-`top`. Router: z = Wr x with float32 sums, s = sigmoid(z); the choice is made on s + correction (a
+`top`. Router: z = Wr x with float32 sums (one of the library's products writing float32), s = sigmoid(z); the choice is made on s + correction (a
 stored vector), the weights use s without it. Experts form `n_groups` equal groups of neighbours;
 a group's score is the sum of its two largest choice scores, and only experts of the `keep_groups`
 best groups can be chosen (the others count as minus infinity). The `top` largest choice scores
@@ -71,10 +71,11 @@ class RoutedExperts(FeedForward):
         self.hidden, self.F, self.E, self.top = hidden, intermediate, experts, top
         self.n_groups, self.keep, self.scale = n_groups, keep_groups, float(scale)
         self.router_name, self.correction_name = router_name, correction_name
+        self.router = Linear([router_name], [experts], hidden)
         self.up_names, self.down_names = list(up_names), list(down_names)
 
     def tensor_specs(self):
-        specs = [TensorSpec(self.router_name, (self.E, self.hidden)), TensorSpec(self.correction_name, (self.E,), init="bias")]
+        specs = self.router.tensor_specs() + [TensorSpec(self.correction_name, (self.E,), init="bias")]
         for u, d in zip(self.up_names, self.down_names):
             specs += [TensorSpec(u, (self.F, self.hidden)), TensorSpec(d, (self.hidden, self.F))]
         return specs
@@ -84,12 +85,12 @@ class RoutedExperts(FeedForward):
         return self.E * self.hidden + self.E + self.top * 2 * self.F * self.hidden
 
     def bind(self, tensors, dtype, device):
-        self.router = tensors[self.router_name]
+        self.router.bind(tensors, dtype, device)
         self.correction = tensors[self.correction_name].float().contiguous()
         self.w_up = torch.stack([tensors[n] for n in self.up_names]).contiguous()        # [E, F, hidden]
         self.w_down = torch.stack([tensors[n] for n in self.down_names]).contiguous()    # [E, hidden, F]
         self.counts = torch.zeros((self.E,), dtype=torch.int32, device=device)
-        if self.router.dtype != dtype or self.w_up.dtype != dtype:
+        if self.w_up.dtype != dtype:
             raise ValueError(f"the experts' matrices are {self.w_up.dtype}, the engine runs in {dtype}")
 
     def _on_tensor_cores(self, x) -> bool:
@@ -103,7 +104,8 @@ class RoutedExperts(FeedForward):
         pairs = T * self.top
         idx = torch.empty((T, self.top), dtype=torch.int32, device=dev)
         wgt = torch.empty((T, self.top), dtype=torch.float32, device=dev)
-        k.moe_route(x, self.router, self.correction, idx, wgt, self.n_groups, self.keep, self.top, self.scale)
+        z = self.router.forward(x, ctx, out_dtype=torch.float32)                  # logits, float32 sums
+        k.moe_route(z, self.correction, idx, wgt, self.n_groups, self.keep, self.top, self.scale)
         if pairs <= self.PAIRS_ONE_BY_ONE:
             hid = torch.empty((pairs, self.F), dtype=x.dtype, device=dev)
             out = torch.empty((self.top, T, self.hidden), dtype=torch.float32, device=dev)

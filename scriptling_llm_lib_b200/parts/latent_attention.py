@@ -11,7 +11,11 @@ Only c and the rotated key part are cached: one vector of kv_rank + rot_dim per 
 the number of heads (a cache unit with one key "head" of that width and no value storage). Keys
 and values are never formed per position. Since q_i . (Wuk_i c) = (Wuk_i^T q_i) . c, a head asks
 the cached vectors with [Wuk_i^T q_i | q_rot] directly, sums the latents with the softmax weights,
-and applies Wuv_i once to that sum. All heads of a row read the same cached rows.
+and applies Wuv_i once to that sum. All heads of a row read the same cached rows. That is the form
+of decode steps and of portions that land on a cache. A prompt step whose sequences all start at
+position 0 forms keys and values per head for its own rows instead (two products over the step's
+latents) and runs the library's attention kernel for keys and values of one width on them: fewer
+products per query and key than asking the latent, which is wider than a head.
 
 A layer built with `shares_cache=True` has no Wdkv: it runs with `writes=False` on the unit another
 latent-attention layer of the same widths and rotation wrote, with its own Wq, Wuk, Wuv and Wo.
@@ -50,6 +54,8 @@ class LatentAttention(Mixer):
         else:
             self.proj = Linear([q_name, dkv_name], [qw, kv_rank + rot_dim], hidden)
         self.out = Linear([o_name], [hidden], n_heads * v_dim)
+        self.kv_up = Linear([uk_name, uv_name], [n_heads * dim, n_heads * v_dim], kv_rank)
+        self.hd = (max(dim + rot_dim, v_dim) + 3) // 4 * 4      # one width for keys, values and queries of the per-head form
         self.uk_name, self.uv_name, self.dkv_norm_name = uk_name, uv_name, dkv_norm_name
 
     def tensor_specs(self):
@@ -63,6 +69,17 @@ class LatentAttention(Mixer):
         self.proj.bind(tensors, dtype, device)
         self.out.bind(tensors, dtype, device)
         self.wuk, self.wuv = tensors[self.uk_name], tensors[self.uv_name]
+        self.kv_up.bind(tensors, dtype, device)
+        # the output matrix with zero columns where the per-head form pads a head's values to `hd`
+        if self.hd != self.V:
+            w = self.out.weight
+            wide = torch.zeros((w.shape[0], self.H, self.hd), dtype=w.dtype, device=w.device)
+            wide[:, :, :self.V] = w.view(w.shape[0], self.H, self.V)
+            self.out_wide = self.out.rows(0, w.shape[0])
+            self.out_wide.in_features = self.H * self.hd
+            self.out_wide.weight = wide.view(w.shape[0], self.H * self.hd)
+        else:
+            self.out_wide = self.out
         self.norm_w = None if self.shares_cache else tensors[self.dkv_norm_name].float().contiguous()
 
     def prepare(self, max_positions, device):
@@ -80,6 +97,43 @@ class LatentAttention(Mixer):
         blocks = ctx.n_seqs * -(-self.H // 8)
         return max(1, min(-(-2 * ctx.engine.sm_count // blocks), ctx.max_pages * PAGE // 32, 64))
 
+    PER_HEAD_MIN_ROWS = 32       # prompts from position 0 with at least this many rows form keys and values per head
+
+    def _tables(self, ctx):
+        """Pages of their own for the per-head keys and values of a prompt step: every sequence's positions from a
+        page border on; one table for all layers of the step."""
+        made = ctx.scratch.get("latent_heads_table")
+        if made is None:
+            import numpy as np
+            per = [-(-n // PAGE) for n in ctx.seq_lens_host]
+            table = np.zeros((len(per), max(per)), dtype=np.int32)
+            at = 0
+            for b, n in enumerate(per):
+                table[b, :n] = np.arange(at, at + n)
+                at += n
+            made = (torch.from_numpy(table).pin_memory().to(ctx.slots.device, non_blocking=True), at)
+            ctx.scratch["latent_heads_table"] = made
+        return made
+
+    def _per_head(self, q, ctx, pages, block_table):
+        """The prompt from position 0: keys [Wuk c | rotated part] and values Wuv c per head for the step's rows, then
+        the library's attention kernel for keys and values of one width over pages of their own. Costs
+        (dim + rot_dim + v_dim) products per query, key and head instead of (2 kv_rank + rot_dim)."""
+        k = ctx.kernels.mix
+        T, dev = q.shape[0], q.device
+        dense = torch.empty((T, self.R + self.P), dtype=q.dtype, device=dev)
+        k.latent_gather(pages, ctx, block_table, dense)
+        kv = self.kv_up.forward(dense[:, :self.R], ctx)                       # [T, H dim | H v_dim]
+        table, n_pages = self._tables(ctx)
+        kt = torch.empty((n_pages, self.H, PAGE, self.hd), dtype=q.dtype, device=dev)
+        vt = torch.empty((n_pages, self.H, PAGE, self.hd), dtype=q.dtype, device=dev)
+        qt = torch.empty((T, self.H * self.hd), dtype=q.dtype, device=dev)
+        k.latent_heads(q, kv, dense, self.R, ctx, table, kt, vt, qt, self.H, self.D, self.P, self.V, self.hd)
+        attn = torch.empty((T, self.H * self.hd), dtype=q.dtype, device=dev)
+        ctx.kernels.attn_paged(qt, attn, ctx.seq_start, ctx.seq_pos0, table, kt, vt, ctx.n_seqs, ctx.max_new, self.H, self.H,
+                               self.hd, None, self.scale)
+        return self.out_wide.forward(attn, ctx, partials_ok=True)
+
     def forward(self, x, ctx, unit, writes):
         if writes == self.shares_cache:
             raise ValueError("a latent-attention layer writes the cache unit exactly when it has a down-projection of its own")
@@ -95,13 +149,16 @@ class LatentAttention(Mixer):
                 raise ValueError("latent attention rotates adjacent pairs")
         k.latent_store(q, self.H, self.D, proj[:, self.q_width:] if writes else None, self.norm_w, self.eps, table, rot, ctx,
                        block_table, pages if writes else None, self.R, self.P)
+        if ctx.from_start and not ctx.is_decode and ctx.max_new >= self.PER_HEAD_MIN_ROWS:
+            return self._per_head(q, ctx, pages, block_table)
         qa = torch.empty((T, self.H, self.R + self.P), dtype=torch.float32, device=x.device)
         k.latent_absorb(q, self.wuk, qa, self.H, self.D, self.P, self.R, self.scale)
         n_split = self.splits(ctx)
         part = torch.empty((T, self.H, n_split, self.R + 2), dtype=torch.float32, device=x.device)
         k.latent_attn(qa, pages, ctx, block_table, part, self.H, self.R, self.P, n_split)
         attn = torch.empty((T, self.H * self.V), dtype=x.dtype, device=x.device)
-        k.latent_expand(part, self.wuv, attn, self.H, self.V, self.R, n_split)
+        olat = torch.empty((T, self.H, self.R), dtype=torch.float32, device=x.device)
+        k.latent_expand(part, olat, self.wuv, attn, self.H, self.V, self.R, n_split)
         return self.out.forward(attn, ctx, partials_ok=True)
 
 

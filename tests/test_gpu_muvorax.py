@@ -341,7 +341,7 @@ def test_the_router_against_the_plain_choice():
         want_idx, want_w = plain.route(h.double(), Wd, "r.", {"experts": E, "top": top, "scale": 1.7, "groups": {"count": groups, "keep": keep}})
         idx = torch.empty((50, top), dtype=torch.int32, device="cuda")
         wgt = torch.empty((50, top), dtype=torch.float32, device="cuda")
-        k.moe_route(h.cuda(), wr.cuda(), corr.cuda(), idx, wgt, groups, keep, top, 1.7)
+        k.moe_route((h @ wr.T).cuda().contiguous(), corr.cuda(), idx, wgt, groups, keep, top, 1.7)
         for t in range(50):
             got = dict(zip(idx[t].tolist(), wgt[t].tolist()))
             want = dict(zip(want_idx[t].tolist(), want_w[t].tolist()))
