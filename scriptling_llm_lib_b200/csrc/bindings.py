@@ -338,8 +338,10 @@ class TensorCoreGemm:
 
     SKINNY_MAX_M = 128
 
-    def gemm_grouped(self, a, w, out, tile_group, err_flag):
-        """out[M, N] = a[M, K] @ w[g]^T with w [G, N, K] and the 128 rows of `a` from row 128 t on multiplied by
+    ACTS = {None: 0, "gelu_tanh": 1, "relu_squared": 2, "silu": 3}
+
+    def gemm_grouped(self, a, w, out, tile_group, err_flag, act=None):
+        """out[M, N] = act(a[M, K] @ w[g]^T) with w [G, N, K] and the 128 rows of `a` from row 128 t on multiplied by
         matrix tile_group[t] (int32 on the device, M / 128 entries): rows laid out so that no 128 hold two groups."""
         M, K = a.shape
         G, N = w.shape[0], w.shape[1]
@@ -350,7 +352,19 @@ class TensorCoreGemm:
         fn.restype = c_int
         _check(fn(_ptr(a, torch.bfloat16, "a"), _ptr(w, torch.bfloat16, "w"), _ptr(out, None, "out"), c_int(M), c_int(N), c_int(K),
                   c_int(K), c_int(K), c_int(N), c_int(1 if out.dtype == torch.float32 else 0), _ptr(tile_group, torch.int32, "tile_group"),
-                  c_int(G), _ptr(err_flag, torch.int32, "err_flag"), _stream()), "gemm_grouped")
+                  c_int(G), c_int(self.ACTS[act]), _ptr(err_flag, torch.int32, "err_flag"), _stream()), "gemm_grouped")
+
+    def gemm_act(self, a, w, out, err_flag, act: str):
+        """out[M, N] = act(a @ w^T): the activation on the float sums, in the product's epilogue."""
+        M, K = a.shape
+        N = w.shape[0]
+        if w.shape[1] != K or tuple(out.shape) != (M, N) or not out.is_contiguous() or out.dtype not in (torch.bfloat16, torch.float32):
+            raise KernelError(f"gemm_act shapes: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)} {out.dtype}")
+        fn = self.lib.sllm_gemm_tc_act_bf16
+        fn.restype = c_int
+        _check(fn(c_void_p(a.data_ptr()), c_void_p(w.data_ptr()), c_void_p(out.data_ptr()), c_int(M), c_int(N), c_int(K),
+                  c_int(a.stride(0)), c_int(w.stride(0)), c_int(N), c_int(1 if out.dtype == torch.float32 else 0), c_int(self.ACTS[act]),
+                  _ptr(err_flag, torch.int32, "err_flag"), _stream()), "gemm_act")
 
     def gemm_skinny(self, a, w, out, err_flag, swiglu=False):
         """The same product for at most 128 rows of `a`, with the weights as the tensor cores' 128-row

@@ -49,7 +49,21 @@ struct TcFold {
   // of A from row 128 t on are multiplied by matrix tile_group[t]. Null: one matrix for all rows.
   const int* tile_group;
   int group_rows;
+  // an activation applied to the float sums before they are stored (the plain store only): 0 none, 1 the tanh form of
+  // gelu, 2 the square of relu, 3 silu
+  int act;
 };
+
+__device__ __forceinline__ void tc_act32(uint32_t (&r)[32], int act) {
+#pragma unroll
+  for (int j = 0; j < 32; j++) {
+    float v = __uint_as_float(r[j]);
+    if (act == 1) v = 0.5f * v * (1.0f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)));
+    else if (act == 2) v = v > 0.f ? v * v : 0.f;
+    else v = v / (1.0f + expf(-v));
+    r[j] = __float_as_uint(v);
+  }
+}
 
 // the scale a row is owed by a folded norm before the product: its partial sums added in their order
 __device__ __forceinline__ float tc_row_scale(const TcFold& fd, int row, int M) {
@@ -253,6 +267,7 @@ __device__ __forceinline__ void tc_epilogue_tile(uint32_t acc, int q, int lane, 
       tmem_ld32(acc + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, r);
       asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
       if (owed) tc_scale32(r, rs);
+      if (EPI == TC_EPI_STORE && fd.act) tc_act32(r, fd.act);
       if (row < M) tc_store_row<EPI>(C, row, n0 + c0, N, ldc, out_f32, r);
     }
   }
@@ -709,20 +724,46 @@ SLLM_EXPORT int sllm_gemm_tc_fold_bf16(const void* A, const void* B, void* C, in
 // 0 .. n_groups - 1). The caller lays the rows of A out so that no tile holds rows of two groups. The one-SM kernel
 // (tiles of 128 rows); a tile's columns beyond N read the next group's rows and are not written.
 SLLM_EXPORT int sllm_gemm_tc_grouped_bf16(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb, int ldc,
-                                          int out_f32, const int* tile_group, int n_groups, int* err, cudaStream_t stream) {
+                                          int out_f32, const int* tile_group, int n_groups, int act, int* err, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if (K <= 0 || (K & 7) || (lda & 7) || (ldb & 7) || ((uintptr_t)A & 15) || ((uintptr_t)B & 15) || !tile_group || n_groups < 1)
     return SLLM_ERR_ARG;
   if ((long long)n_groups * N > 0x7fffffffLL) return SLLM_ERR_ARG;
   TcFold fd{};
+  if (act < 0 || act > 3) return SLLM_ERR_ARG;
   fd.tile_group = tile_group;
   fd.group_rows = N;
+  fd.act = act;
   const TcRope rp{};
   CUtensorMap ma, mb;
   int big = N > 128;
   int rc = tc_make_map(&ma, A, M, K, lda, TC_BM);
   if (rc) return rc;
   rc = tc_make_map(&mb, B, n_groups * N, K, ldb, big ? 256 : 128);
+  if (rc) return rc;
+  return big ? tc_launch<256, 4, TC_EPI_STORE>(ma, mb, C, M, N, K, ldc, out_f32, err, stream, rp, fd)
+             : tc_launch<128, 6, TC_EPI_STORE>(ma, mb, C, M, N, K, ldc, out_f32, err, stream, rp, fd);
+}
+
+// C[M,N] = act(A[M,K] B[N,K]^T): the plain store with an activation on the float sums (1 the tanh form of gelu, 2 the
+// square of relu, 3 silu), on the kernel the sizes choose as for the plain product.
+SLLM_EXPORT int sllm_gemm_tc_act_bf16(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb, int ldc,
+                                      int out_f32, int act, int* err, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (K <= 0 || (K & 7) || (lda & 7) || (ldb & 7) || ((uintptr_t)A & 15) || ((uintptr_t)B & 15) || act < 1 || act > 3) return SLLM_ERR_ARG;
+  TcFold fd{};
+  fd.act = act;
+  const TcRope rp{};
+  CUtensorMap ma, mb;
+  int big = N > 128;
+  int rc = tc_make_map(&ma, A, M, K, lda, TC_BM);
+  if (rc) return rc;
+  if (tc_use_pair(M, N)) {
+    rc = tc_make_map(&mb, B, N, K, ldb, 128);
+    if (rc) return rc;
+    return tc_pair_launch<6, TC_EPI_STORE>(ma, mb, C, M, N, K, ldc, out_f32, err, stream, rp, fd);
+  }
+  rc = tc_make_map(&mb, B, N, K, ldb, big ? 256 : 128);
   if (rc) return rc;
   return big ? tc_launch<256, 4, TC_EPI_STORE>(ma, mb, C, M, N, K, ldc, out_f32, err, stream, rp, fd)
              : tc_launch<128, 6, TC_EPI_STORE>(ma, mb, C, M, N, K, ldc, out_f32, err, stream, rp, fd);

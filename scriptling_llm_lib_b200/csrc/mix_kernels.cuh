@@ -45,11 +45,42 @@ struct DytArgs {
   int d;
 };
 
+template <typename A> __device__ __forceinline__ float4 ld4_flag(const void* p, int is_f32, size_t i) {
+  return is_f32 ? ld4((const float*)p + i) : ld4((const A*)p + i);
+}
+
 template <typename A>
-__global__ void dyt_add_norm_kernel(DytArgs p) {
+__global__ void dyt_add_norm_kernel(DytArgs p, int vec) {
   int r = blockIdx.x;
   size_t in = p.rows ? (size_t)p.rows[r] : (size_t)r;
   bool update = p.rows == nullptr && p.y != nullptr;
+  if (vec) {                                      // four elements a thread: d and every buffer's start are multiples of four
+    for (int j = (blockIdx.y * blockDim.x + threadIdx.x) * 4; j < p.d; j += gridDim.y * blockDim.x * 4) {
+      float4 v = *(const float4*)(p.x + in * p.d + j);
+      if (p.y) {
+        float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int k = 0; k < p.n_parts; k++) {
+          float4 t = ld4_flag<A>(p.y, p.y_f32, (size_t)k * p.part_stride + in * p.d + j);
+          a.x += t.x; a.y += t.y; a.z += t.z; a.w += t.w;
+        }
+        if (p.has_post) {
+          float4 w = *(const float4*)((const float*)p.pw + j), b = *(const float4*)((const float*)p.pb + j);
+          a.x = tanhf(p.palpha * a.x) * w.x + b.x; a.y = tanhf(p.palpha * a.y) * w.y + b.y;
+          a.z = tanhf(p.palpha * a.z) * w.z + b.z; a.w = tanhf(p.palpha * a.w) * w.w + b.w;
+        }
+        v.x += a.x; v.y += a.y; v.z += a.z; v.w += a.w;
+        if (update) *(float4*)(p.x + in * p.d + j) = v;
+      }
+      if (p.out) {
+        float4 w = *(const float4*)((const float*)p.w + j), b = *(const float4*)((const float*)p.b + j);
+        float4 y = make_float4(tanhf(p.alpha * v.x) * w.x + b.x, tanhf(p.alpha * v.y) * w.y + b.y, tanhf(p.alpha * v.z) * w.z + b.z,
+                               tanhf(p.alpha * v.w) * w.w + b.w);
+        if (p.out_f32) st4((float*)p.out + (size_t)r * p.d + j, y);
+        else st4((A*)p.out + (size_t)r * p.d + j, y);
+      }
+    }
+    return;
+  }
   for (int j = blockIdx.y * blockDim.x + threadIdx.x; j < p.d; j += gridDim.y * blockDim.x) {
     float v = p.x[in * p.d + j];
     if (p.y) {
@@ -65,13 +96,23 @@ __global__ void dyt_add_norm_kernel(DytArgs p) {
 
 // ------------------------------------------------------------------ activations in place
 // kind 1: the tanh form of gelu; 2: the square of relu; 3: silu
+__device__ __forceinline__ float act_f(float z, int kind) {
+  return kind == 1 ? gelu_tanh_f(z) : kind == 2 ? (z > 0.f ? z * z : 0.f) : silu_f(z);
+}
 template <typename A>
-__global__ void act_inplace_kernel(A* __restrict__ x, long long n, int kind) {
+__global__ void act_inplace_kernel(A* __restrict__ x, long long n, int kind, int vec) {
   long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (vec) {                                      // eight elements a thread: n and the buffer's start are multiples of eight
+    i *= 8;
+    if (i >= n) return;
+    F8 v = ld8(x + i);
+#pragma unroll
+    for (int e = 0; e < 8; e++) v.f[e] = act_f(v.f[e], kind);
+    st8(x + i, v);
+    return;
+  }
   if (i >= n) return;
-  float z = to_f32(x[i]);
-  float y = kind == 1 ? gelu_tanh_f(z) : kind == 2 ? (z > 0.f ? z * z : 0.f) : silu_f(z);
-  x[i] = from_f32<A>(y);
+  x[i] = from_f32<A>(act_f(to_f32(x[i]), kind));
 }
 
 // ------------------------------------------------------------------ linear attention with a decay per head

@@ -49,6 +49,14 @@ class ActFeedForward(FeedForward):
         self.down.bind(tensors, dtype, device)
 
     def forward(self, x, ctx):
+        w = self.up.weight
+        if x.dtype == torch.bfloat16 and w.dtype == x.dtype:
+            tc = ctx.kernels.tensor_core
+            if x.shape[0] > tc.SKINNY_MAX_M and tc.takes(x, w) and not ctx.kernels.decode.prefers(x, w, ctx.engine.sm_count):
+                # a long step: the activation rides in the tensor-core product's epilogue, on the float sums
+                h = torch.empty((x.shape[0], self.intermediate), dtype=x.dtype, device=x.device)
+                tc.gemm_act(x, w, h, ctx.err_flag, self.act)
+                return self.down.forward(h, ctx, partials_ok=True)
         h = self.up.forward(x, ctx)
         ctx.kernels.mix.act_inplace(h, self.act)
         return self.down.forward(h, ctx, partials_ok=True)
@@ -130,8 +138,7 @@ class RoutedExperts(FeedForward):
         k.moe_gather_rows(x, pair_of_row, self.top, xs)
         tc = ctx.kernels.tensor_core
         hid = torch.empty((rows, self.F), dtype=x.dtype, device=dev)
-        tc.gemm_grouped(xs, self.w_up, hid, tile_group, ctx.err_flag)
-        k.act_inplace(hid, "relu_squared")
+        tc.gemm_grouped(xs, self.w_up, hid, tile_group, ctx.err_flag, act="relu_squared")
         ys = torch.empty((rows, self.hidden), dtype=torch.float32, device=dev)
         tc.gemm_grouped(hid, self.w_down, ys, tile_group, ctx.err_flag)
         out = torch.empty((T, self.hidden), dtype=torch.float32, device=dev)
