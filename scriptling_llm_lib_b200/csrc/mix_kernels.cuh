@@ -121,8 +121,11 @@ __global__ void act_inplace_kernel(A* __restrict__ x, long long n, int kind, int
 // walks the sequence's rows in pieces of at most C rows. Within a piece of n rows (decay^m written g^m):
 //   P[i][j] = g^(i-j) q_i . k_j (j <= i);  o_i = g^(i+1) S^T q_i + sum_j P[i][j] v_j;
 //   S <- g^n S + sum_j g^(n-1-j) k_j v_j^T.
-// All in float32 out of shared memory, 4 x 4 outputs a thread. The state [slot][head][D][V] is read at the start
-// and written at the end.
+// All in float32 out of shared memory, 4 x 4 outputs a thread. Warps 0-3 do this work; warps 4-7 fetch the next
+// piece's rows meanwhile (SiLU applied) into the other of two buffers. The state [slot][head][D][V] is read at the
+// start and written at the end.
+__device__ __forceinline__ void bar_compute() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
 template <typename A>
 __global__ void __launch_bounds__(256) lin_attn_decay_kernel(const A* __restrict__ proj, int ld, int q_col, int k_col, int v_col,
                                                              const float* __restrict__ decay, float* __restrict__ state,
@@ -133,49 +136,70 @@ __global__ void __launch_bounds__(256) lin_attn_decay_kernel(const A* __restrict
   int vt = min(VT, V - c0);
   int Dp = (D + 3) & ~3, VTp = (VT + 3) & ~3;
   int qs_ld = Dp + 4;
+  size_t qk_size = (size_t)C * qs_ld, v_size = (size_t)C * VTp;
   float* S = sm;                                  // [Dp][VTp]
-  float* qs = S + (size_t)Dp * VTp;               // [C][qs_ld]
-  float* ks = qs + (size_t)C * qs_ld;             // [C][qs_ld]
-  float* vs = ks + (size_t)C * qs_ld;             // [C][VTp]
-  float* P = vs + (size_t)C * VTp;                // [C][C]
+  float* qs0 = S + (size_t)Dp * VTp;              // two buffers of [C][qs_ld] queries, [C][qs_ld] keys, [C][VTp] values
+  float* P = qs0 + 2 * (2 * qk_size + v_size);    // [C][C]
   float* pw = P + (size_t)C * C;                  // [C + 2] powers of the decay
   int tid = threadIdx.x;
+  bool loader = tid >= 128;
+  int ct = tid & 127;                             // index among the computing (or the fetching) threads
   float g = decay[h];
   if (tid == 0) {
     float a = 1.f;
     for (int i = 0; i <= C + 1; i++) { pw[i] = a; a *= g; }
   }
   float* st = state + ((size_t)slots[b] * H + h) * D * V;
-  for (int i = tid; i < Dp * VTp; i += 256) {
-    int d = i / VTp, c = i % VTp;
-    S[i] = (d < D && c < vt) ? st[(size_t)d * V + c0 + c] : 0.f;
-  }
   int r_begin = seq_start[b], r_end = seq_start[b + 1];
-  for (int r0 = r_begin; r0 < r_end; r0 += C) {
+  int n_pieces = (r_end - r_begin + C - 1) / C;
+
+  auto stage = [&](int piece) {
+    float* qs = qs0 + (size_t)(piece & 1) * (2 * qk_size + v_size);
+    float* ks = qs + qk_size;
+    float* vs = ks + qk_size;
+    int r0 = r_begin + piece * C;
     int n = min(C, r_end - r0);
-    __syncthreads();
-    for (int i = tid; i < C * Dp; i += 256) {
-      int r = i / Dp, d = i % Dp;
-      float qv = 0.f, kv = 0.f;
-      if (r < n && d < D) {
-        const A* row = proj + (size_t)(r0 + r) * ld + (size_t)h * D + d;
-        qv = silu_f(to_f32(row[q_col]));
-        kv = silu_f(to_f32(row[k_col]));
+    int lane = ct & 31, w = ct >> 5;
+    for (int r = w; r < C; r += 4) {
+      const A* row = proj + (size_t)(r0 + r) * ld + (size_t)h * D;
+      for (int d = lane; d < Dp; d += 32) {
+        float qv = 0.f, kv = 0.f;
+        if (r < n && d < D) {
+          qv = silu_f(to_f32(row[q_col + d]));
+          kv = silu_f(to_f32(row[k_col + d]));
+        }
+        qs[r * qs_ld + d] = qv;
+        ks[r * qs_ld + d] = kv;
       }
-      qs[r * qs_ld + d] = qv;
-      ks[r * qs_ld + d] = kv;
+      const A* vrow = proj + (size_t)(r0 + r) * ld + v_col + (size_t)h * V + c0;
+      for (int c = lane; c < VTp; c += 32) vs[r * VTp + c] = (r < n && c < vt) ? silu_f(to_f32(vrow[c])) : 0.f;
     }
-    for (int i = tid; i < C * VTp; i += 256) {
-      int r = i / VTp, c = i % VTp;
-      float vv = 0.f;
-      if (r < n && c < vt) vv = silu_f(to_f32(proj[(size_t)(r0 + r) * ld + v_col + (size_t)h * V + c0 + c]));
-      vs[i] = vv;
+  };
+
+  if (loader) {
+    if (n_pieces > 0) stage(0);
+  } else {
+    for (int i = ct; i < Dp * VTp; i += 128) {
+      int d = i / VTp, c = i % VTp;
+      S[i] = (d < D && c < vt) ? st[(size_t)d * V + c0 + c] : 0.f;
     }
-    __syncthreads();
+  }
+  __syncthreads();
+  for (int piece = 0; piece < n_pieces; piece++) {
+    if (loader) {
+      if (piece + 1 < n_pieces) stage(piece + 1);
+      __syncthreads();
+      continue;
+    }
+    const float* qs = qs0 + (size_t)(piece & 1) * (2 * qk_size + v_size);
+    const float* ks = qs + qk_size;
+    const float* vs = ks + qk_size;
+    int r0 = r_begin + piece * C;
+    int n = min(C, r_end - r0);
     // scores inside the piece
-    for (int i = tid; i < C * C; i += 256) {
+    for (int i = ct; i < C * C; i += 128) {
       int qi = i / C, kj = i % C;
-      float s = 0.f;
+      float sc = 0.f;
       if (kj <= qi && qi < n) {
         const float4* a = (const float4*)(qs + qi * qs_ld);
         const float4* bb = (const float4*)(ks + kj * qs_ld);
@@ -185,14 +209,14 @@ __global__ void __launch_bounds__(256) lin_attn_decay_kernel(const A* __restrict
           s0 += x.x * y.x + x.z * y.z;
           s1 += x.y * y.y + x.w * y.w;
         }
-        s = (s0 + s1) * pw[qi - kj];
+        sc = (s0 + s1) * pw[qi - kj];
       }
-      P[i] = s;
+      P[i] = sc;
     }
-    __syncthreads();
+    bar_compute();
     // outputs of the piece: 4 rows x 4 columns a thread
     int n4 = (n + 3) / 4, c4 = VTp / 4;
-    for (int it = tid; it < n4 * c4; it += 256) {
+    for (int it = ct; it < n4 * c4; it += 128) {
       int i0 = (it / c4) * 4, cc = (it % c4) * 4;
       float acc[4][4];
 #pragma unroll
@@ -231,11 +255,11 @@ __global__ void __launch_bounds__(256) lin_attn_decay_kernel(const A* __restrict
           if (cc + c < vt) orow[c] = acc[a][c];
       }
     }
-    __syncthreads();
+    bar_compute();
     // the state after the piece: 4 key dims x 4 columns a thread
     float gn = pw[n];
     int d4 = Dp / 4;
-    for (int it = tid; it < d4 * c4; it += 256) {
+    for (int it = ct; it < d4 * c4; it += 128) {
       int d0 = (it / c4) * 4, cc = (it % c4) * 4;
       float acc[4][4];
 #pragma unroll
@@ -257,12 +281,13 @@ __global__ void __launch_bounds__(256) lin_attn_decay_kernel(const A* __restrict
       for (int a = 0; a < 4; a++)
         *(float4*)(S + (size_t)(d0 + a) * VTp + cc) = make_float4(acc[a][0], acc[a][1], acc[a][2], acc[a][3]);
     }
+    __syncthreads();
   }
-  __syncthreads();
-  for (int i = tid; i < Dp * VTp; i += 256) {
-    int d = i / VTp, c = i % VTp;
-    if (d < D && c < vt) st[(size_t)d * V + c0 + c] = S[i];
-  }
+  if (!loader)
+    for (int i = ct; i < Dp * VTp; i += 128) {
+      int d = i / VTp, c = i % VTp;
+      if (d < D && c < vt) st[(size_t)d * V + c0 + c] = S[i];
+    }
 }
 
 // ------------------------------------------------------------------ read-out norm over the whole row with a gate
