@@ -126,11 +126,62 @@ __global__ void act_inplace_kernel(A* __restrict__ x, long long n, int kind, int
 // start and written at the end.
 __device__ __forceinline__ void bar_compute() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
+// A tile [rows][cols_p] of SiLU(src) into shared memory by 128 threads (`lt` among them): src rows `ld` apart, rows
+// r >= n and columns c >= cols are zero. All loads of a batch are asked for before the first is used, so that a tile
+// costs a few trips to memory and not one per element. vec: eight elements a load (cols a multiple of 8 and equal to
+// cols_p, every row's start 16-byte aligned).
+template <typename A>
+__device__ __forceinline__ void stage_silu_tile(float* __restrict__ dst, int dst_ld, const A* __restrict__ src, int ld, int n,
+                                                int rows, int cols, int cols_p, int lt, int vec) {
+  if (vec) {
+    int chunks = cols_p / 8, total = rows * chunks;
+    for (int base = 0; base < total; base += 128 * 4) {
+      F8 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; u++) {
+        int i = base + u * 128 + lt;
+        int r = i / chunks, c = (i % chunks) * 8;
+        if (i < total && r < n) v[u] = ld8(src + (size_t)r * ld + c);
+        else {
+#pragma unroll
+          for (int e = 0; e < 8; e++) v[u].f[e] = 0.f;
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 4; u++) {
+        int i = base + u * 128 + lt;
+        if (i >= total) continue;
+        int r = i / chunks, c = (i % chunks) * 8;
+        float* d = dst + (size_t)r * dst_ld + c;
+        *(float4*)d = make_float4(silu_f(v[u].f[0]), silu_f(v[u].f[1]), silu_f(v[u].f[2]), silu_f(v[u].f[3]));
+        *(float4*)(d + 4) = make_float4(silu_f(v[u].f[4]), silu_f(v[u].f[5]), silu_f(v[u].f[6]), silu_f(v[u].f[7]));
+      }
+    }
+    return;
+  }
+  int total = rows * cols_p;
+  for (int base = 0; base < total; base += 128 * 8) {
+    float v[8];
+#pragma unroll
+    for (int u = 0; u < 8; u++) {
+      int i = base + u * 128 + lt;
+      int r = i / cols_p, c = i % cols_p;
+      v[u] = (i < total && r < n && c < cols) ? to_f32(src[(size_t)r * ld + c]) : 0.f;
+    }
+#pragma unroll
+    for (int u = 0; u < 8; u++) {
+      int i = base + u * 128 + lt;
+      if (i < total) dst[(size_t)(i / cols_p) * dst_ld + i % cols_p] = silu_f(v[u]);
+    }
+  }
+}
+
 template <typename A>
 __global__ void __launch_bounds__(256) lin_attn_decay_kernel(const A* __restrict__ proj, int ld, int q_col, int k_col, int v_col,
                                                              const float* __restrict__ decay, float* __restrict__ state,
                                                              const int* __restrict__ seq_start, const int* __restrict__ slots,
-                                                             float* __restrict__ o, int H, int D, int V, int VT, int C) {
+                                                             float* __restrict__ o, int H, int D, int V, int VT, int C,
+                                                             int vec_qk, int vec_v) {
   extern __shared__ __align__(16) float sm[];
   int b = blockIdx.z, h = blockIdx.y, c0 = blockIdx.x * VT;
   int vt = min(VT, V - c0);
@@ -159,21 +210,10 @@ __global__ void __launch_bounds__(256) lin_attn_decay_kernel(const A* __restrict
     float* vs = ks + qk_size;
     int r0 = r_begin + piece * C;
     int n = min(C, r_end - r0);
-    int lane = ct & 31, w = ct >> 5;
-    for (int r = w; r < C; r += 4) {
-      const A* row = proj + (size_t)(r0 + r) * ld + (size_t)h * D;
-      for (int d = lane; d < Dp; d += 32) {
-        float qv = 0.f, kv = 0.f;
-        if (r < n && d < D) {
-          qv = silu_f(to_f32(row[q_col + d]));
-          kv = silu_f(to_f32(row[k_col + d]));
-        }
-        qs[r * qs_ld + d] = qv;
-        ks[r * qs_ld + d] = kv;
-      }
-      const A* vrow = proj + (size_t)(r0 + r) * ld + v_col + (size_t)h * V + c0;
-      for (int c = lane; c < VTp; c += 32) vs[r * VTp + c] = (r < n && c < vt) ? silu_f(to_f32(vrow[c])) : 0.f;
-    }
+    const A* base = proj + (size_t)r0 * ld;
+    stage_silu_tile<A>(qs, qs_ld, base + q_col + (size_t)h * D, ld, n, C, D, Dp, ct, vec_qk);
+    stage_silu_tile<A>(ks, qs_ld, base + k_col + (size_t)h * D, ld, n, C, D, Dp, ct, vec_qk);
+    stage_silu_tile<A>(vs, VTp, base + v_col + (size_t)h * V + c0, ld, n, C, vt, VTp, ct, vec_v && vt == VTp);
   };
 
   if (loader) {
@@ -196,63 +236,98 @@ __global__ void __launch_bounds__(256) lin_attn_decay_kernel(const A* __restrict
     const float* vs = ks + qk_size;
     int r0 = r_begin + piece * C;
     int n = min(C, r_end - r0);
-    // scores inside the piece
-    for (int i = ct; i < C * C; i += 128) {
-      int qi = i / C, kj = i % C;
-      float sc = 0.f;
-      if (kj <= qi && qi < n) {
-        const float4* a = (const float4*)(qs + qi * qs_ld);
-        const float4* bb = (const float4*)(ks + kj * qs_ld);
-        float s0 = 0.f, s1 = 0.f;
+    // scores inside the piece: 2 x 2 a thread (C is even), blocks above the diagonal are left at zero
+    int c2 = C / 2;
+    for (int it = ct; it < c2 * c2; it += 128) {
+      int qi = (it / c2) * 2, kj = (it % c2) * 2;
+      float s00 = 0.f, s01 = 0.f, s10 = 0.f, s11 = 0.f;
+      if (kj <= qi + 1 && qi < n) {
+        const float4* a0 = (const float4*)(qs + qi * qs_ld);
+        const float4* a1 = (const float4*)(qs + (qi + 1) * qs_ld);
+        const float4* b0 = (const float4*)(ks + kj * qs_ld);
+        const float4* b1 = (const float4*)(ks + (kj + 1) * qs_ld);
         for (int d = 0; d < Dp / 4; d++) {
-          float4 x = a[d], y = bb[d];
-          s0 += x.x * y.x + x.z * y.z;
-          s1 += x.y * y.y + x.w * y.w;
+          float4 x0 = a0[d], x1 = a1[d], y0 = b0[d], y1 = b1[d];
+          s00 += (x0.x * y0.x + x0.y * y0.y) + (x0.z * y0.z + x0.w * y0.w);
+          s01 += (x0.x * y1.x + x0.y * y1.y) + (x0.z * y1.z + x0.w * y1.w);
+          s10 += (x1.x * y0.x + x1.y * y0.y) + (x1.z * y0.z + x1.w * y0.w);
+          s11 += (x1.x * y1.x + x1.y * y1.y) + (x1.z * y1.z + x1.w * y1.w);
         }
-        sc = (s0 + s1) * pw[qi - kj];
+        s00 = kj <= qi ? s00 * pw[qi - kj] : 0.f;
+        s01 = kj + 1 <= qi ? s01 * pw[qi - kj - 1] : 0.f;
+        s10 = s10 * pw[min(qi + 1 - kj, C)];
+        s11 = kj <= qi ? s11 * pw[qi - kj] : 0.f;
+        if (qi + 1 >= n) { s10 = 0.f; s11 = 0.f; }
       }
-      P[i] = sc;
+      P[qi * C + kj] = s00; P[qi * C + kj + 1] = s01;
+      P[(qi + 1) * C + kj] = s10; P[(qi + 1) * C + kj + 1] = s11;
     }
     bar_compute();
-    // outputs of the piece: 4 rows x 4 columns a thread
-    int n4 = (n + 3) / 4, c4 = VTp / 4;
-    for (int it = ct; it < n4 * c4; it += 128) {
-      int i0 = (it / c4) * 4, cc = (it % c4) * 4;
-      float acc[4][4];
+    // outputs of the piece: RT rows x 4 columns a thread, RT = 4 where that gives every thread work, else 1
+    int c4 = VTp / 4;
+    if (((n + 3) / 4) * c4 >= 128) {
+      int n4 = (n + 3) / 4;
+      for (int it = ct; it < n4 * c4; it += 128) {
+        int i0 = (it / c4) * 4, cc = (it % c4) * 4;
+        float acc[4][4];
 #pragma unroll
-      for (int a = 0; a < 4; a++)
+        for (int a = 0; a < 4; a++)
 #pragma unroll
-        for (int c = 0; c < 4; c++) acc[a][c] = 0.f;
-      for (int d = 0; d < D; d++) {
-        float4 sv = *(const float4*)(S + (size_t)d * VTp + cc);
+          for (int c = 0; c < 4; c++) acc[a][c] = 0.f;
+        for (int d = 0; d < D; d++) {
+          float4 sv = *(const float4*)(S + (size_t)d * VTp + cc);
+#pragma unroll
+          for (int a = 0; a < 4; a++) {
+            float qv = (i0 + a < C) ? qs[(i0 + a) * qs_ld + d] : 0.f;
+            acc[a][0] += qv * sv.x; acc[a][1] += qv * sv.y; acc[a][2] += qv * sv.z; acc[a][3] += qv * sv.w;
+          }
+        }
 #pragma unroll
         for (int a = 0; a < 4; a++) {
-          float qv = (i0 + a < C) ? qs[(i0 + a) * qs_ld + d] : 0.f;
-          acc[a][0] += qv * sv.x; acc[a][1] += qv * sv.y; acc[a][2] += qv * sv.z; acc[a][3] += qv * sv.w;
+          float f = pw[min(i0 + a + 1, C + 1)];
+#pragma unroll
+          for (int c = 0; c < 4; c++) acc[a][c] *= f;
         }
-      }
+        int jmax = min(i0 + 3, n - 1);
+        for (int j = 0; j <= jmax; j++) {
+          float4 vv = *(const float4*)(vs + (size_t)j * VTp + cc);
 #pragma unroll
-      for (int a = 0; a < 4; a++) {
-        float f = pw[min(i0 + a + 1, C + 1)];
-#pragma unroll
-        for (int c = 0; c < 4; c++) acc[a][c] *= f;
-      }
-      int jmax = min(i0 + 3, n - 1);
-      for (int j = 0; j <= jmax; j++) {
-        float4 vv = *(const float4*)(vs + (size_t)j * VTp + cc);
+          for (int a = 0; a < 4; a++) {
+            float pv = (i0 + a < C) ? P[(i0 + a) * C + j] : 0.f;      // zero above the diagonal
+            acc[a][0] += pv * vv.x; acc[a][1] += pv * vv.y; acc[a][2] += pv * vv.z; acc[a][3] += pv * vv.w;
+          }
+        }
 #pragma unroll
         for (int a = 0; a < 4; a++) {
-          float pv = (i0 + a < C) ? P[(i0 + a) * C + j] : 0.f;      // zero above the diagonal
-          acc[a][0] += pv * vv.x; acc[a][1] += pv * vv.y; acc[a][2] += pv * vv.z; acc[a][3] += pv * vv.w;
+          if (i0 + a >= n) continue;
+          float* orow = o + (size_t)(r0 + i0 + a) * H * V + (size_t)h * V + c0 + cc;
+#pragma unroll
+          for (int c = 0; c < 4; c++)
+            if (cc + c < vt) orow[c] = acc[a][c];
         }
       }
-#pragma unroll
-      for (int a = 0; a < 4; a++) {
-        if (i0 + a >= n) continue;
-        float* orow = o + (size_t)(r0 + i0 + a) * H * V + (size_t)h * V + c0 + cc;
-#pragma unroll
-        for (int c = 0; c < 4; c++)
-          if (cc + c < vt) orow[c] = acc[a][c];
+    } else {
+      for (int it = ct; it < n * c4; it += 128) {
+        int i = it / c4, cc = (it % c4) * 4;
+        float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+        const float* qrow = qs + i * qs_ld;
+        for (int d = 0; d < D; d++) {
+          float4 sv = *(const float4*)(S + (size_t)d * VTp + cc);
+          float qv = qrow[d];
+          a0 += qv * sv.x; a1 += qv * sv.y; a2 += qv * sv.z; a3 += qv * sv.w;
+        }
+        float f = pw[i + 1];
+        a0 *= f; a1 *= f; a2 *= f; a3 *= f;
+        for (int j = 0; j <= i; j++) {
+          float4 vv = *(const float4*)(vs + (size_t)j * VTp + cc);
+          float pv = P[i * C + j];
+          a0 += pv * vv.x; a1 += pv * vv.y; a2 += pv * vv.z; a3 += pv * vv.w;
+        }
+        float* orow = o + (size_t)(r0 + i) * H * V + (size_t)h * V + c0 + cc;
+        if (cc < vt) orow[0] = a0;
+        if (cc + 1 < vt) orow[1] = a1;
+        if (cc + 2 < vt) orow[2] = a2;
+        if (cc + 3 < vt) orow[3] = a3;
       }
     }
     bar_compute();
@@ -465,22 +540,29 @@ __global__ void __launch_bounds__(256) latent_attn_kernel(const float* __restric
     const A* tile_src = pages + ((size_t)pt[k0 / SLLM_PAGE] * SLLM_PAGE + k0 % SLLM_PAGE) * W;
     constexpr int VEC = 16 / sizeof(A);
     if (vec) {
-      int chunks = W / VEC;
-      for (int i = threadIdx.x; i < 32 * chunks; i += nthreads) {
-        int kr = i / chunks, d = (i % chunks) * VEC;
-        float* dst = Ks + kr * Wp + d;
-        if (kr < nk) {
+      int chunks = W / VEC, total = 32 * chunks;
+      for (int base = 0; base < total; base += 4 * nthreads) {       // four loads a thread in flight
+        uint4 raw[4];
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+          int i = base + u * nthreads + threadIdx.x;
+          int kr = i / chunks, d = (i % chunks) * VEC;
+          raw[u] = (i < total && kr < nk) ? *(const uint4*)(tile_src + (size_t)kr * W + d) : make_uint4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+          int i = base + u * nthreads + threadIdx.x;
+          if (i >= total) continue;
+          int kr = i / chunks, d = (i % chunks) * VEC;
+          float* dst = Ks + kr * Wp + d;
           if constexpr (sizeof(A) == 2) {
-            F8 f = ld8((const bf16*)(tile_src + (size_t)kr * W + d));
+            const __nv_bfloat162* h2 = (const __nv_bfloat162*)&raw[u];
 #pragma unroll
-            for (int e = 0; e < 8; e++) dst[e] = f.f[e];
+            for (int e = 0; e < 4; e++) { dst[2 * e] = __low2float(h2[e]); dst[2 * e + 1] = __high2float(h2[e]); }
           } else {
-            float4 f = *(const float4*)(tile_src + (size_t)kr * W + d);
-            dst[0] = f.x; dst[1] = f.y; dst[2] = f.z; dst[3] = f.w;
+            dst[0] = __uint_as_float(raw[u].x); dst[1] = __uint_as_float(raw[u].y);
+            dst[2] = __uint_as_float(raw[u].z); dst[3] = __uint_as_float(raw[u].w);
           }
-        } else {
-#pragma unroll
-          for (int e = 0; e < VEC; e++) dst[e] = 0.f;
         }
       }
     } else {
@@ -623,25 +705,42 @@ __global__ void __launch_bounds__(256) selective_scan_kernel(ScanArgs p) {
           *c_s = b_s + MIX_SCAN_ROWS * N;
     int r0 = r_begin + chunk * MIX_SCAN_ROWS;
     int n = min(MIX_SCAN_ROWS, r_end - r0);
-    for (int i = lt; i < MIX_SCAN_ROWS * 32; i += 128) {
+    // all loads of the chunk first (4 rows of 32 channels a thread, then the rows' B and C), the arithmetic behind them
+    float dtr[4], xr[4], zr[4];
+#pragma unroll
+    for (int u = 0; u < 4; u++) {
+      int i = lt + 128 * u;
       int r = i >> 5, ch = ch0 + (i & 31);
-      float dt = 0.f, xv = 0.f, zv = 0.f;
-      if (r < n && ch < p.I) {
-        dt = softplus_f(p.dt_raw[(size_t)(r0 + r) * p.lddt + ch] + load_w(p.dt_bias, p.w_f32, ch));
-        xv = to_f32(xs[(size_t)(r0 + r) * p.ldx + ch]);
-        zv = silu_f(to_f32(zs[(size_t)(r0 + r) * p.ldz + ch]));
-      }
-      dt_s[i] = dt; x_s[i] = xv; z_s[i] = zv;
+      bool ok = r < n && ch < p.I;
+      dtr[u] = ok ? p.dt_raw[(size_t)(r0 + r) * p.lddt + ch] + load_w(p.dt_bias, p.w_f32, ch) : 0.f;
+      xr[u] = ok ? to_f32(xs[(size_t)(r0 + r) * p.ldx + ch]) : 0.f;
+      zr[u] = ok ? to_f32(zs[(size_t)(r0 + r) * p.ldz + ch]) : 0.f;
     }
-    for (int i = lt; i < MIX_SCAN_ROWS * N; i += 128) {
-      int r = i / N, nn = i % N;
-      float bv = 0.f, cv = 0.f;
-      if (r < n) {
+    for (int base = 0; base < MIX_SCAN_ROWS * N; base += 128 * 4) {
+      float bv[4], cv[4];
+#pragma unroll
+      for (int u = 0; u < 4; u++) {
+        int i = base + lt + 128 * u;
+        int r = i / N, nn = i % N;
+        bool ok = i < MIX_SCAN_ROWS * N && r < n;
         const A* row = bcs + (size_t)(r0 + r) * p.ldbc;
-        bv = to_f32(row[p.b_col + nn]);
-        cv = to_f32(row[p.c_col + nn]);
+        bv[u] = ok ? to_f32(row[p.b_col + nn]) : 0.f;
+        cv[u] = ok ? to_f32(row[p.c_col + nn]) : 0.f;
       }
-      b_s[i] = bv; c_s[i] = cv;
+#pragma unroll
+      for (int u = 0; u < 4; u++) {
+        int i = base + lt + 128 * u;
+        if (i < MIX_SCAN_ROWS * N) { b_s[i] = bv[u]; c_s[i] = cv[u]; }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 4; u++) {
+      int i = lt + 128 * u;
+      int r = i >> 5, ch = ch0 + (i & 31);
+      bool ok = r < n && ch < p.I;
+      dt_s[i] = ok ? softplus_f(dtr[u]) : 0.f;
+      x_s[i] = xr[u];
+      z_s[i] = ok ? silu_f(zr[u]) : 0.f;
     }
   };
 
@@ -673,6 +772,7 @@ __global__ void __launch_bounds__(256) selective_scan_kernel(ScanArgs p) {
                   *c_s = b_s + MIX_SCAN_ROWS * N;
       int r0 = r_begin + chunk * MIX_SCAN_ROWS;
       int n = min(MIX_SCAN_ROWS, r_end - r0);
+#pragma unroll 4
       for (int r = 0; r < n; r++) {
         float dt = dt_s[r * 32 + cc], xv = x_s[r * 32 + cc];
         float dx = dt * xv;
