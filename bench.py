@@ -671,6 +671,167 @@ def sequence_kernels_alone(args):
     return 0
 
 
+def mix_kernels_alone(args):
+    """The kernels of the Muvorax decoder's mixers and feed-forwards, each alone at MUVORAX_SIZES[--design-sizes or w2048]:
+    a prompt of --prefill-tokens rows and a decode step of --batch rows at --context; a JSON line each with the time
+    (CUDA events around a captured run of launches whose inputs rotate through more than L2 holds where they are small)
+    and what it is of the HBM copy rate or of the float FMA rate (bf16 tensor rate for the grouped products)."""
+    import torch
+    from types import SimpleNamespace
+    from scriptling_llm_lib_b200.csrc.bindings import KernelSet, ProbeKernels
+    pk = peaks()
+    z = MUVORAX_SIZES[(args.design_sizes or "w2048").split(",")[0]]
+    dt = {"bfloat16": torch.bfloat16, "float32": torch.float32}[args.dtype]
+    ks = KernelSet(dt)
+    k = ks.mix
+    fma = ProbeKernels().fma_tflops()
+    dev = "cuda"
+    esz = 2 if dt == torch.bfloat16 else 4
+    W, H, D, P, V, R = z["width"], z["heads"], z["dim"], z["rot_dim"], z["vdim"], z["rank"]
+    LH, LD, LV = W // 128, 128, 128
+    I, N, K = 2 * W, 16, W // 16
+    E, top, F = z["experts"], z["top"], z["expert_ff"]
+
+    def timed(launch, n_sets, reps=8):
+        side = torch.cuda.Stream()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(side):
+            for i in range(2):
+                launch(i % n_sets)
+            torch.cuda.synchronize()
+            with torch.cuda.graph(graph, stream=side):
+                for i in range(reps):
+                    launch(i % n_sets)
+        for _ in range(2):
+            graph.replay()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(3):
+            graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / (3 * reps) * 1e3
+
+    def report(name, rows, us, nbytes=None, flops=None, tensor=False):
+        rec = {"kernel": name, "rows": rows, "us": round(us, 1)}
+        if nbytes is not None:
+            rec.update(gbs=round(nbytes / us / 1e3, 1), of_hbm=round(nbytes / us / 1e3 / pk["hbm_gbs"], 3))
+        if flops is not None and tensor:
+            rec.update(tflops=round(flops / us / 1e6, 1), of_bf16=round(flops / us / 1e6 / pk["bf16_tflops"], 3))
+        elif flops is not None:
+            rec.update(tflops=round(flops / us / 1e6, 2), of_fma=round(flops / us / 1e6 / fma, 3))
+        print(json.dumps(rec), flush=True)
+
+    for label, lens, ctxlen in (("prompt", [args.prefill_tokens], args.prefill_tokens), ("decode", [1] * args.batch, args.context)):
+        T, B = sum(lens), len(lens)
+        start = [0]
+        for n in lens:
+            start.append(start[-1] + n)
+        pages = -(-ctxlen // 64)
+        c = SimpleNamespace(
+            seq_start=torch.tensor(start, dtype=torch.int32, device=dev),
+            tok_seq=torch.repeat_interleave(torch.arange(B, dtype=torch.int32, device=dev), torch.tensor(lens, device=dev)).int(),
+            slots=torch.arange(B, dtype=torch.int32, device=dev), n_seqs=B, max_new=max(lens), engine=SimpleNamespace(sm_count=148),
+            tok_pos=(torch.arange(T, dtype=torch.int32, device=dev) if T != B else
+                     torch.full((B,), ctxlen - 1, dtype=torch.int32, device=dev)))
+        n_sets = 4 if T > 64 else 24
+        # ---- residual sum with a normed addend + norm
+        xs = [torch.randn(T, W, device=dev) for _ in range(n_sets)]
+        ad = [torch.randn(T, W, device=dev).to(dt) for _ in range(n_sets)]
+        wn, bn = torch.ones(W, device=dev), torch.zeros(W, device=dev)
+        y = torch.empty(T, W, dtype=dt, device=dev)
+        us = timed(lambda i: k.dyt_add_norm(xs[i], ad[i], (wn, bn, 0.9), None, wn, bn, 1.1, y), n_sets)
+        report(f"dyt_add_norm ({label})", T, us, nbytes=T * W * (4 + 4 + esz + esz))
+        # ---- linear attention with a decay per head, and its gated read-out norm
+        proj = [(torch.randn(T, 2 * LH * LD + 2 * LH * LV, device=dev) * 0.5).to(dt) for _ in range(n_sets)]
+        decay = torch.full((LH,), 0.99, device=dev)
+        n_st = 1 if T > 64 else n_sets
+        S = [torch.zeros(B + 1, LH, LD, LV, device=dev) for _ in range(n_st)]
+        o = torch.empty(T, LH * LV, device=dev)
+        us = timed(lambda i: k.lin_attn_decay(proj[i], 0, LH * LD, 2 * LH * LD, decay, S[i % n_st], c, o, LH, LD, LV), n_sets)
+        report(f"lin_attn_decay heads {LH} x {LD} x {LV} ({label})", T, us, nbytes=(2 * B * LH * LD * LV * 4 if T == B else None),
+               flops=2 * T * LH * (2 * LD * LV + 16 * (LD + LV)))
+        yo = torch.empty(T, LH * LV, dtype=dt, device=dev)
+        us = timed(lambda i: k.gated_row_rms(o, proj[i][:, 2 * LH * LD + LH * LV:], wn[:1].expand(LH * LV).contiguous(), yo, 1e-6, "sigmoid"), n_sets)
+        report(f"gated_row_rms ({label})", T, us, nbytes=T * LH * LV * (4 + esz + esz))
+        # ---- the selective scan
+        xz = [(torch.randn(T, 2 * I, device=dev) * 0.5).to(dt) for _ in range(n_sets)]
+        dtr = torch.randn(T, I, device=dev)
+        bc = torch.randn(T, K + 2 * N, device=dev).to(dt)
+        zero_i, a_log = torch.zeros(I, device=dev), torch.zeros(I, N, device=dev)
+        Ss = [torch.zeros(B + 1, I, N, device=dev) for _ in range(n_st)]
+        ys = torch.empty(T, I, dtype=dt, device=dev)
+        us = timed(lambda i: k.selective_scan(xz[i][:, :I], dtr, zero_i, a_log, zero_i + 1, bc, K, K + N, xz[i][:, I:], Ss[i % n_st], c, ys, I, N), n_sets)
+        report(f"selective_scan inner {I} states {N} ({label})", T, us,
+               nbytes=T * I * (4 + 3 * esz) + (2 * B * I * N * 4 if T == B else 0), flops=6 * T * I * N)
+        # ---- attention over the cached latent
+        Wl = R + P
+        lat = torch.randn(B * pages + 1, 1, 64, Wl, device=dev).to(dt)
+        table = torch.arange(B * pages, dtype=torch.int32, device=dev).view(B, pages).contiguous()
+        q = (torch.randn(T, H * (D + P), device=dev) * 0.3).to(dt)
+        wuk, wuv = (torch.randn(H * D, R, device=dev) * 0.05).to(dt), (torch.randn(H * V, R, device=dev) * 0.05).to(dt)
+        qa = torch.empty(T, H, Wl, device=dev)
+        us = timed(lambda i: k.latent_absorb(q, wuk, qa, H, D, P, R, 0.07), 1)
+        report(f"latent_absorb ({label})", T, us, nbytes=(H * D * R * esz if T == B else None), flops=2 * T * H * D * R)
+        if T == B:
+            n_split = max(1, min(-(-2 * 148 // (B * -(-H // 8))), pages * 2, 64))
+            part = torch.empty(T, H, n_split, R + 2, device=dev)
+            us = timed(lambda i: k.latent_attn(qa, lat, c, table, part, H, R, P, n_split), 1)
+            report(f"latent_attn rank {R} + {P}, {n_split} splits ({label})", T, us, nbytes=B * ctxlen * Wl * esz,
+                   flops=2 * B * H * ctxlen * (2 * R + P))
+            olat = torch.empty(T, H, R, device=dev)
+            ao = torch.empty(T, H * V, dtype=dt, device=dev)
+            us = timed(lambda i: k.latent_expand(part, olat, wuv, ao, H, V, R, n_split), 1)
+            report(f"latent_expand ({label})", T, us, nbytes=H * V * R * esz + T * H * n_split * R * 4)
+        else:
+            hd = D + P
+            kt = torch.randn(pages, H, 64, hd, device=dev).to(dt)
+            qt = torch.randn(T, H * hd, device=dev).to(dt)
+            ot = torch.empty(T, H * hd, dtype=dt, device=dev)
+            zero_b = torch.zeros(B, dtype=torch.int32, device=dev)
+            us = timed(lambda i: ks.attn_paged(qt, ot, c.seq_start, zero_b, table, kt, kt, B, T, H, H, hd, None, 0.07), 1)
+            report(f"attn_paged per head, width {hd} ({label}, keys and values made from the latent)", T, us, flops=2 * H * T * T * hd)
+        # ---- routed experts
+        h = (torch.randn(T, W, device=dev) * 0.5).to(dt)
+        zl = torch.randn(T, E, device=dev)
+        corr = torch.zeros(E, device=dev)
+        idx = torch.empty(T, top, dtype=torch.int32, device=dev)
+        wgt = torch.empty(T, top, device=dev)
+        us = timed(lambda i: k.moe_route(zl, corr, idx, wgt, z["n_groups"], z["keep"], top, 2.5), 1)
+        report(f"moe_route {E} experts ({label})", T, us)
+        w_up = (torch.randn(E, F, W, device=dev) * 0.02).to(dt)
+        w_down = (torch.randn(E, W, F, device=dev) * 0.02).to(dt)
+        pairs = T * top
+        if pairs <= 64:
+            hid = torch.empty(pairs, F, dtype=dt, device=dev)
+            out = torch.empty(top, T, W, device=dev)
+            us = timed(lambda i: k.moe_pairs(h, w_up, w_down, idx, wgt, hid, out), 1)
+            report(f"moe_pairs {pairs} pairs, experts {W} x {F} ({label})", T, us, nbytes=pairs * 2 * F * W * esz)
+        elif dt == torch.bfloat16:
+            rows = -(-(pairs + E * 127) // 128) * 128
+            counts = torch.zeros(E, dtype=torch.int32, device=dev)
+            offsets = torch.empty(E + 1, dtype=torch.int32, device=dev)
+            por = torch.empty(rows, dtype=torch.int32, device=dev)
+            rop = torch.empty(pairs, dtype=torch.int32, device=dev)
+            tg = torch.empty(rows // 128, dtype=torch.int32, device=dev)
+            xs2 = torch.empty(rows, W, dtype=dt, device=dev)
+            hid = torch.empty(rows, F, dtype=dt, device=dev)
+            ys2 = torch.empty(rows, W, device=dev)
+            out = torch.empty(T, W, device=dev)
+            err = torch.zeros(1, dtype=torch.int32, device=dev)
+            tc = ks.tensor_core
+            us = timed(lambda i: (k.moe_group_rows(idx, counts, offsets, por, rop, tg, pad=128), k.moe_gather_rows(h, por, top, xs2)), 1)
+            report(f"moe_group_rows + moe_gather_rows ({label})", T, us, nbytes=rows * W * esz * 2)
+            us = timed(lambda i: tc.gemm_grouped(xs2, w_up, hid, tg, err, act="relu_squared", rows_used=offsets[E:]), 1)
+            report(f"gemm_grouped up, {rows} rows for {pairs} pairs ({label})", T, us, flops=2 * pairs * F * W, tensor=True)
+            us = timed(lambda i: tc.gemm_grouped(hid, w_down, ys2, tg, err, rows_used=offsets[E:]), 1)
+            report(f"gemm_grouped down ({label})", T, us, flops=2 * pairs * F * W, tensor=True)
+            us = timed(lambda i: k.moe_combine(ys2, rop, wgt, out), 1)
+            report(f"moe_combine ({label})", T, us, nbytes=(pairs + T) * W * 4)
+    return 0
+
+
 def kernel_alone(args):
     """One decode kernel by itself, as profiles/ quotes it: launched back to back in a CUDA graph over
     inputs that rotate through more bytes than L2 holds, timed with CUDA events; one JSON line per case.
@@ -776,9 +937,11 @@ def main():
     ap.add_argument("--no-shapes", dest="shapes", action="store_false", help="skip the Llama-3.2-1B and Llama-3.1-8B sizes")
     ap.add_argument("--only", default="all", choices=["all", "prefill", "decode"],
                     help="run one part only (a small case to profile); the JSON line then holds that part alone")
-    ap.add_argument("--kernel", default=None, choices=["attn_decode", "gemm_small_m", "sequence"],
+    ap.add_argument("--kernel", default=None, choices=["attn_decode", "gemm_small_m", "sequence", "mix"],
                     help="time one decode kernel alone at --shape, --batch (and --context) instead of the model; 'sequence': "
-                         "the kernels of the mixers with state at --design-sizes, for a prompt and for a decode step")
+                         "the kernels of the mixers with state at --design-sizes, for a prompt and for a decode step; 'mix': "
+                         "the same for the kernels of latent attention, decayed linear attention, the selective scan and "
+                         "routed experts")
     ap.add_argument("--design", default=None, choices=sorted(DESIGNS),
                     help="measure this design's prompt step and decoding at a few real layer sizes beside the Llama decoder "
                          "of equal size (--prefill-tokens, --batch, --context, --steps, --dtype, --only apply) instead of the "
@@ -795,6 +958,8 @@ def main():
     args.warmup = max(3, args.warmup)
     if args.kernel == "sequence":
         return sequence_kernels_alone(args)
+    if args.kernel == "mix":
+        return mix_kernels_alone(args)
     if args.kernel is not None:
         return kernel_alone(args)
     if args.design is not None:

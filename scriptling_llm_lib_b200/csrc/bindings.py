@@ -340,9 +340,10 @@ class TensorCoreGemm:
 
     ACTS = {None: 0, "gelu_tanh": 1, "relu_squared": 2, "silu": 3}
 
-    def gemm_grouped(self, a, w, out, tile_group, err_flag, act=None):
+    def gemm_grouped(self, a, w, out, tile_group, err_flag, act=None, rows_used=None):
         """out[M, N] = act(a[M, K] @ w[g]^T) with w [G, N, K] and the 128 rows of `a` from row 128 t on multiplied by
-        matrix tile_group[t] (int32 on the device, M / 128 entries): rows laid out so that no 128 hold two groups."""
+        matrix tile_group[t] (int32 on the device, M / 128 entries): rows laid out so that no 128 hold two groups.
+        rows_used: an int32 on the device (one element), how many of the M rows hold anything; the rest is not worked."""
         M, K = a.shape
         G, N = w.shape[0], w.shape[1]
         if (w.dim() != 3 or w.shape[2] != K or tuple(out.shape) != (M, N) or a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16
@@ -352,7 +353,8 @@ class TensorCoreGemm:
         fn.restype = c_int
         _check(fn(_ptr(a, torch.bfloat16, "a"), _ptr(w, torch.bfloat16, "w"), _ptr(out, None, "out"), c_int(M), c_int(N), c_int(K),
                   c_int(K), c_int(K), c_int(N), c_int(1 if out.dtype == torch.float32 else 0), _ptr(tile_group, torch.int32, "tile_group"),
-                  c_int(G), c_int(self.ACTS[act]), _ptr(err_flag, torch.int32, "err_flag"), _stream()), "gemm_grouped")
+                  c_int(G), c_int(self.ACTS[act]), _ptr(rows_used, torch.int32, "rows_used"),
+                  _ptr(err_flag, torch.int32, "err_flag"), _stream()), "gemm_grouped")
 
     def gemm_act(self, a, w, out, err_flag, act: str):
         """out[M, N] = act(a @ w^T): the activation on the float sums, in the product's epilogue."""

@@ -49,6 +49,7 @@ struct TcFold {
   // of A from row 128 t on are multiplied by matrix tile_group[t]. Null: one matrix for all rows.
   const int* tile_group;
   int group_rows;
+  const int* m_used;      // (or null) on the device: the rows of A that hold anything; tiles behind them are not worked
   // an activation applied to the float sums before they are stored (the plain store only): 0 none, 1 the tanh form of
   // gelu, 2 the square of relu, 3 silu
   int act;
@@ -370,6 +371,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   const uint32_t full0 = smem_u32(bars), empty0 = full0 + 8 * STAGES, acc_full0 = empty0 + 8 * STAGES, acc_empty0 = acc_full0 + 16;
 
   int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (fd.m_used) M = min(M, *fd.m_used);     // the same number for every thread of every block: all walk the same tiles
   const int tiles_m = (M + TC_BM - 1) / TC_BM, tiles_n = (N + BN - 1) / BN, n_tiles = tiles_m * tiles_n;
   const int nkb = (K + TC_BK - 1) / TC_BK;
 
@@ -722,9 +724,11 @@ SLLM_EXPORT int sllm_gemm_tc_fold_bf16(const void* A, const void* B, void* C, in
 // Grouped rows: C[M,N] = A[M,K] B_g^T with B [n_groups * N, K] holding one [N, K] matrix per group and the 128 rows
 // of A from row 128 t on multiplied by matrix tile_group[t] (int32 on the device, ceil(M / 128) entries, each in
 // 0 .. n_groups - 1). The caller lays the rows of A out so that no tile holds rows of two groups. The one-SM kernel
-// (tiles of 128 rows); a tile's columns beyond N read the next group's rows and are not written.
+// (tiles of 128 rows); a tile's columns beyond N read the next group's rows and are not written. m_used (or null): an
+// int on the device, the rows of A in use; the tiles behind them are left alone (their number is known on the device only).
 SLLM_EXPORT int sllm_gemm_tc_grouped_bf16(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb, int ldc,
-                                          int out_f32, const int* tile_group, int n_groups, int act, int* err, cudaStream_t stream) {
+                                          int out_f32, const int* tile_group, int n_groups, int act, const int* m_used, int* err,
+                                          cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if (K <= 0 || (K & 7) || (lda & 7) || (ldb & 7) || ((uintptr_t)A & 15) || ((uintptr_t)B & 15) || !tile_group || n_groups < 1)
     return SLLM_ERR_ARG;
@@ -734,6 +738,7 @@ SLLM_EXPORT int sllm_gemm_tc_grouped_bf16(const void* A, const void* B, void* C,
   fd.tile_group = tile_group;
   fd.group_rows = N;
   fd.act = act;
+  fd.m_used = m_used;
   const TcRope rp{};
   CUtensorMap ma, mb;
   int big = N > 128;

@@ -138,9 +138,9 @@ class RoutedExperts(FeedForward):
         k.moe_gather_rows(x, pair_of_row, self.top, xs)
         tc = ctx.kernels.tensor_core
         hid = torch.empty((rows, self.F), dtype=x.dtype, device=dev)
-        tc.gemm_grouped(xs, self.w_up, hid, tile_group, ctx.err_flag, act="relu_squared")
+        tc.gemm_grouped(xs, self.w_up, hid, tile_group, ctx.err_flag, act="relu_squared", rows_used=offsets[self.E:])
         ys = torch.empty((rows, self.hidden), dtype=torch.float32, device=dev)
-        tc.gemm_grouped(hid, self.w_down, ys, tile_group, ctx.err_flag)
+        tc.gemm_grouped(hid, self.w_down, ys, tile_group, ctx.err_flag, rows_used=offsets[self.E:])
         out = torch.empty((T, self.hidden), dtype=torch.float32, device=dev)
         k.moe_combine(ys, row_of_pair, wgt, out)
         return out
