@@ -73,6 +73,12 @@ CFG_C = config([with_ff(mamba(24, 40, 8, 4), moe(12, 5, 1, 1, 1, 3.0)), with_ff(
                 with_ff(latent(1, 20, 2, 32, 130, 0.5, 20.0), dense(24))], width=40, vocab=77)
 
 
+# widths that are multiples of nothing: every vector path has to step aside
+CFG_D = config([with_ff(latent(3, 5, 2, 3, 9, 0.6, 30.0), moe(6, 3, 2, 1, 1, 1.2)), with_ff(mamba(10, 1, 1, 2), dense(14)),
+                with_ff(lightning(1, 5, 7, (0.9,)), moe(10, 6, 1, 3, 1, 0.5)), latent(1, 3, 6, 5, 9, 0.4, 30.0, dims=2, kv_from=0),
+                mamba(6, 3, 2, 5)], width=50, vocab=61)
+
+
 def random_weights(cfg, seed, std=0.25):
     """Weights by tensor name for `cfg`, bfloat16-representable (the folder stores bfloat16)."""
     from scriptling_llm_lib_b200 import models  # noqa: F401
@@ -146,7 +152,7 @@ def rel(got, want):
 def folders(tmp_path_factory):
     root = tmp_path_factory.mktemp("muvorax")
     out = {}
-    for name, cfg, seed in (("A", CFG_A, 1), ("B", CFG_B, 2), ("C", CFG_C, 3)):
+    for name, cfg, seed in (("A", CFG_A, 1), ("B", CFG_B, 2), ("C", CFG_C, 3), ("D", CFG_D, 4)):
         W = random_weights(cfg, seed)
         out[name] = (write_folder(root / name, cfg, W), cfg, W)
     return out
@@ -157,7 +163,7 @@ def plain_logits(cfg, W, tokens, rnd=plain.ident, layers_out=None):
 
 
 # --------------------------------------------------------------------------- whole models
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_a_whole_prompt_equals_the_plain_statement_in_32_bit(folders, name):
     folder, cfg, W = folders[name]
     tokens = ids(90, cfg["vocab"], 10)
@@ -166,7 +172,7 @@ def test_a_whole_prompt_equals_the_plain_statement_in_32_bit(folders, name):
     assert rel(got, want) < TOL_F32
 
 
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_bfloat16_stays_near_the_plain_statement_that_rounds_where_the_engine_stores(folders, name):
     folder, cfg, W = folders[name]
     tokens = ids(70, cfg["vocab"], 11)
@@ -217,7 +223,7 @@ def test_each_mechanism_alone(tmp_path, layer):
 
 
 # --------------------------------------------------------------------------- cutting, batches, slots
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_token_by_token_and_portions_equal_the_whole_prompt(folders, name):
     folder, cfg, W = folders[name]
     tokens = ids(150, cfg["vocab"], 14)
