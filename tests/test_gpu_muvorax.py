@@ -75,7 +75,7 @@ CFG_C = config([with_ff(mamba(24, 40, 8, 4), moe(12, 5, 1, 1, 1, 3.0)), with_ff(
 
 # widths that are multiples of nothing: every vector path has to step aside
 CFG_D = config([with_ff(latent(3, 5, 2, 3, 9, 0.6, 30.0), moe(6, 3, 2, 1, 1, 1.2)), with_ff(mamba(10, 1, 1, 2), dense(14)),
-                with_ff(lightning(1, 5, 7, (0.9,)), moe(10, 6, 1, 3, 1, 0.5)), latent(1, 3, 6, 5, 9, 0.4, 30.0, dims=2, kv_from=0),
+                with_ff(lightning(1, 5, 7, (0.9,)), moe(10, 6, 1, 3, 1, 0.5)), latent(1, 3, 2, 5, 9, 0.4, 30.0, kv_from=0),
                 mamba(6, 3, 2, 5)], width=50, vocab=61)
 
 
