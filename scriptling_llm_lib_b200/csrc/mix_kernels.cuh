@@ -609,6 +609,109 @@ __global__ void __launch_bounds__(256) latent_attn_kernel(const float* __restric
   }
 }
 
+// The same with 16-byte accesses to shared memory, for widths that are multiples of four (R and R + P): the tile's row
+// stride is a multiple of four floats and an odd number of 16-byte groups (lanes that read different rows hit different
+// banks), a lane scores its key four dims a load, and in the sum over the latent it owns groups of four neighbouring
+// columns (4 lane + 128 i). Four times fewer loads from shared memory per multiply-add than the kernel above.
+template <typename A, int NV4>
+__global__ void __launch_bounds__(256) latent_attn_vec_kernel(const float* __restrict__ qa, const A* __restrict__ pages,
+                                                              const int* __restrict__ tok_pos, const int* __restrict__ tok_seq,
+                                                              const int* __restrict__ block_table, int max_pages,
+                                                              float* __restrict__ part, int H, int R, int P, int n_split, int Wp) {
+  extern __shared__ __align__(16) float sm[];
+  int W = R + P;
+  int t = blockIdx.x, h0 = blockIdx.y * 8, sp = blockIdx.z;
+  int nh = min(8, H - h0);
+  int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  int nthreads = blockDim.x;
+  float* qs = sm;                                 // [8][W]
+  float* Ks = qs + 8 * W;                         // [32][Wp]
+  int pos = tok_pos[t];
+  const int* pt = block_table + (size_t)tok_seq[t] * max_pages;
+  for (int i = threadIdx.x; i < nh * W; i += nthreads) qs[i] = qa[((size_t)t * H + h0) * W + i];
+  int n_tiles = pos / 32 + 1;
+  int per = (n_tiles + n_split - 1) / n_split;
+  int tile_lo = sp * per, tile_hi = min(n_tiles, tile_lo + per);
+  float m = -INFINITY, l = 0.f, acc[NV4][4];
+#pragma unroll
+  for (int i = 0; i < NV4; i++) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+  bool active = wid < nh;
+  const float4* myq = (const float4*)(qs + wid * W);
+  constexpr int VEC = 16 / sizeof(A);
+  for (int tile = tile_lo; tile < tile_hi; tile++) {
+    int k0 = tile * 32;
+    int nk = min(32, pos + 1 - k0);
+    __syncthreads();
+    const A* tile_src = pages + ((size_t)pt[k0 / SLLM_PAGE] * SLLM_PAGE + k0 % SLLM_PAGE) * W;
+    int chunks = W / VEC, total = 32 * chunks;
+    for (int base = 0; base < total; base += 4 * nthreads) {         // four loads a thread in flight
+      uint4 raw[4];
+#pragma unroll
+      for (int u = 0; u < 4; u++) {
+        int i = base + u * nthreads + threadIdx.x;
+        int kr = i / chunks, d = (i % chunks) * VEC;
+        raw[u] = (i < total && kr < nk) ? *(const uint4*)(tile_src + (size_t)kr * W + d) : make_uint4(0, 0, 0, 0);
+      }
+#pragma unroll
+      for (int u = 0; u < 4; u++) {
+        int i = base + u * nthreads + threadIdx.x;
+        if (i >= total) continue;
+        int kr = i / chunks, d = (i % chunks) * VEC;
+        float* dst = Ks + kr * Wp + d;
+        if constexpr (sizeof(A) == 2) {
+          const __nv_bfloat162* h2 = (const __nv_bfloat162*)&raw[u];
+          *(float4*)dst = make_float4(__low2float(h2[0]), __high2float(h2[0]), __low2float(h2[1]), __high2float(h2[1]));
+          *(float4*)(dst + 4) = make_float4(__low2float(h2[2]), __high2float(h2[2]), __low2float(h2[3]), __high2float(h2[3]));
+        } else {
+          *(float4*)dst = make_float4(__uint_as_float(raw[u].x), __uint_as_float(raw[u].y), __uint_as_float(raw[u].z),
+                                      __uint_as_float(raw[u].w));
+        }
+      }
+    }
+    __syncthreads();
+    if (!active) continue;
+    float sc = -INFINITY;
+    if (lane < nk) {
+      const float4* kr = (const float4*)(Ks + lane * Wp);
+      float s0 = 0.f, s1 = 0.f;
+#pragma unroll 4
+      for (int d = 0; d < W / 4; d++) {
+        float4 x = myq[d], y = kr[d];
+        s0 += x.x * y.x + x.y * y.y;
+        s1 += x.z * y.z + x.w * y.w;
+      }
+      sc = s0 + s1;
+    }
+    float m_new = fmaxf(m, warp_max(sc));
+    float c = expf(m - m_new);
+    float pwt = lane < nk ? expf(sc - m_new) : 0.f;
+    l = l * c + warp_sum(pwt);
+    m = m_new;
+#pragma unroll
+    for (int i = 0; i < NV4; i++) { acc[i][0] *= c; acc[i][1] *= c; acc[i][2] *= c; acc[i][3] *= c; }
+    for (int j = 0; j < nk; j++) {
+      float pj = __shfl_sync(0xffffffffu, pwt, j);
+      const float* kr = Ks + j * Wp;
+#pragma unroll
+      for (int i = 0; i < NV4; i++) {
+        int col = 4 * lane + 128 * i;
+        if (col < R) {
+          float4 y = *(const float4*)(kr + col);
+          acc[i][0] += pj * y.x; acc[i][1] += pj * y.y; acc[i][2] += pj * y.z; acc[i][3] += pj * y.w;
+        }
+      }
+    }
+  }
+  if (!active) return;
+  float* dst = part + (((size_t)t * H + h0 + wid) * n_split + sp) * (R + 2);
+  if (lane == 0) { dst[0] = m; dst[1] = l; }
+#pragma unroll
+  for (int i = 0; i < NV4; i++) {
+    int col = 4 * lane + 128 * i;
+    if (col < R) { dst[2 + col] = acc[i][0]; dst[3 + col] = acc[i][1]; dst[4 + col] = acc[i][2]; dst[5 + col] = acc[i][3]; }
+  }
+}
+
 // merge: olat[t][h] = sum_s w_s acc_s / sum_s w_s l_s, w_s = exp(m_s - max m): the splits' sums over the latent as one
 // normalised vector [R] per (row, head).
 __global__ void latent_merge_kernel(const float* __restrict__ part, float* __restrict__ olat, int R, int n_split) {
