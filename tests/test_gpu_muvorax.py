@@ -222,6 +222,22 @@ def test_each_mechanism_alone(tmp_path, layer):
     assert rel(run(eng, [tokens[:20]] + [[t] for t in tokens[20:]]), want) < TOL_F32
 
 
+@pytest.mark.parametrize("rank,heads,dtype", [(160, 2, "float32"), (264, 9, "float32"), (512, 3, "float32"), (256, 4, "bfloat16")])
+def test_wide_latents_token_by_token(tmp_path, rank, heads, dtype):
+    """Latents of several hundred: every lane of the attention kernel owns several groups of columns."""
+    cfg = config([latent(heads, 8, 8, 8, rank, 0.5, 1000.0), with_ff(latent(2, 4, 8, 12, rank, 0.3, 1000.0, kv_from=0), dense(16))],
+                 width=32, vocab=40)
+    W = random_weights(cfg, 9, std=0.4)
+    folder = write_folder(tmp_path / "m", cfg, W)
+    tokens = ids(75, 40, 21)
+    eng = engine(folder, dtype)
+    got = run(eng, [tokens[:3]] + [[t] for t in tokens[3:]])
+    if dtype == "float32":
+        assert rel(got, plain_logits(cfg, W, tokens)) < TOL_F32
+    else:
+        assert rel(got, plain_logits(cfg, W, tokens, rnd=plain.bf16_round)) < TOL_BF16
+
+
 # --------------------------------------------------------------------------- cutting, batches, slots
 @pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_token_by_token_and_portions_equal_the_whole_prompt(folders, name):
