@@ -865,8 +865,8 @@ class MixKernels:
             _ptr(dt_bias, torch.float32, "dt_bias"), _ptr(a_log, torch.float32, "a_log"), _ptr(dskip, torch.float32, "dskip"),
             c_int(1), self._view(bc, "bc"), c_int(bc.stride(0)), c_int(b_col), c_int(c_col), self._view(z, "z"),
             c_int(z.stride(0)), _ptr(state, torch.float32, "state"), _ptr(ctx.seq_start, torch.int32, "seq_start"),
-            _ptr(ctx.slots, torch.int32, "slots"), self._view(out, "out"), c_int(out.stride(0)), c_int(ctx.n_seqs), c_int(inner),
-            c_int(n_state), _stream()), "selective_scan")
+            _ptr(ctx.slots, torch.int32, "slots"), self._view(out, "out"), c_int(out.stride(0)), c_int(ctx.n_seqs),
+            c_int(max(1, ctx.max_new)), c_int(inner), c_int(n_state), _stream()), "selective_scan")
 
     def moe_route(self, z, correction, idx, wgt, n_groups, keep, top, scale):
         """z float32 [T, E] the router's logits -> idx int32 [T, top] the chosen experts, wgt float32 [T, top] their weights."""

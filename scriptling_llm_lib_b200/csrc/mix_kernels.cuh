@@ -770,7 +770,8 @@ __global__ void __launch_bounds__(128) latent_expand_kernel(const float* __restr
 // ------------------------------------------------------------------ the selective scan
 // Per channel c a state S[c][0..N): for each row dt = softplus(dt_raw[c] + dt_bias[c]);
 // S[c][n] <- exp(dt * A[c][n]) * S[c][n] + dt * x[c] * B[n];  y[c] = sum_n S[c][n] * C[n] + D[c] * x[c];  out = y * silu(z[c]),
-// A = -exp(A_log). Four lanes share a channel (every fourth state each); a block takes 32 channels of one sequence and
+// A = -exp(A_log). 4, 8 or 16 lanes share a channel (state n = lane + L i: the more states, the more lanes, so that a row
+// costs a lane few dependent steps and the GPU gets warps enough); a block takes 128 / L channels of one sequence and
 // walks its rows, which a second set of warps stages in shared memory ahead of the walk. x, z, B, C: column slices of
 // buffers of the element type; dt_raw float32.
 struct ScanArgs {
@@ -785,14 +786,15 @@ struct ScanArgs {
   int I, N;
 };
 
-#define MIX_SCAN_ROWS 16      // rows staged at a time
-template <typename A, int NPL>
+template <typename A, int NPL, int L, int MIX_SCAN_ROWS>      // MIX_SCAN_ROWS: rows staged at a time
 __global__ void __launch_bounds__(256) selective_scan_kernel(ScanArgs p) {
-  // Warps 0-3 walk the rows (32 channels x 4 lanes); warps 4-7 stage the next MIX_SCAN_ROWS rows meanwhile: step sizes with
-  // their softplus, inputs, gates with their SiLU (32 channels a row) and the rows' B and C (N each), two buffers in turn.
+  // Warps 0-3 walk the rows: L lanes share a channel (state n = lane + L i), 128 / L channels a block. Warps 4-7 stage the
+  // next MIX_SCAN_ROWS rows meanwhile: step sizes with their softplus, inputs, gates with their SiLU (the block's channels
+  // a row) and the rows' B and C (N each), two buffers in turn.
   extern __shared__ __align__(16) float sm[];
-  const int N = p.N, per_buf = MIX_SCAN_ROWS * (96 + 2 * N);
-  int b = blockIdx.y, ch0 = blockIdx.x * 32;
+  constexpr int CPB = 128 / L;                    // channels a block
+  const int N = p.N, per_buf = MIX_SCAN_ROWS * (3 * CPB + 2 * N);
+  int b = blockIdx.y, ch0 = blockIdx.x * CPB;
   int r_begin = p.seq_start[b], r_end = p.seq_start[b + 1];
   int n_chunks = (r_end - r_begin + MIX_SCAN_ROWS - 1) / MIX_SCAN_ROWS;
   const A* xs = (const A*)p.x;
@@ -804,25 +806,26 @@ __global__ void __launch_bounds__(256) selective_scan_kernel(ScanArgs p) {
 
   auto stage = [&](int chunk) {
     float* buf = sm + (size_t)(chunk & 1) * per_buf;
-    float *dt_s = buf, *x_s = buf + MIX_SCAN_ROWS * 32, *z_s = x_s + MIX_SCAN_ROWS * 32, *b_s = z_s + MIX_SCAN_ROWS * 32,
+    float *dt_s = buf, *x_s = buf + MIX_SCAN_ROWS * CPB, *z_s = x_s + MIX_SCAN_ROWS * CPB, *b_s = z_s + MIX_SCAN_ROWS * CPB,
           *c_s = b_s + MIX_SCAN_ROWS * N;
     int r0 = r_begin + chunk * MIX_SCAN_ROWS;
     int n = min(MIX_SCAN_ROWS, r_end - r0);
-    // all loads of the chunk first (4 rows of 32 channels a thread, then the rows' B and C), the arithmetic behind them
-    float dtr[4], xr[4], zr[4];
+    // all loads of the chunk first, the arithmetic behind them
+    constexpr int PER = (MIX_SCAN_ROWS * CPB + 127) / 128;
+    float dtr[PER], xr[PER], zr[PER];
 #pragma unroll
-    for (int u = 0; u < 4; u++) {
+    for (int u = 0; u < PER; u++) {
       int i = lt + 128 * u;
-      int r = i >> 5, ch = ch0 + (i & 31);
-      bool ok = r < n && ch < p.I;
+      int r = i / CPB, ch = ch0 + i % CPB;
+      bool ok = i < MIX_SCAN_ROWS * CPB && r < n && ch < p.I;
       dtr[u] = ok ? p.dt_raw[(size_t)(r0 + r) * p.lddt + ch] + load_w(p.dt_bias, p.w_f32, ch) : 0.f;
       xr[u] = ok ? to_f32(xs[(size_t)(r0 + r) * p.ldx + ch]) : 0.f;
       zr[u] = ok ? to_f32(zs[(size_t)(r0 + r) * p.ldz + ch]) : 0.f;
     }
-    for (int base = 0; base < MIX_SCAN_ROWS * N; base += 128 * 4) {
-      float bv[4], cv[4];
+    for (int base = 0; base < MIX_SCAN_ROWS * N; base += 128 * 8) {
+      float bv[8], cv[8];
 #pragma unroll
-      for (int u = 0; u < 4; u++) {
+      for (int u = 0; u < 8; u++) {
         int i = base + lt + 128 * u;
         int r = i / N, nn = i % N;
         bool ok = i < MIX_SCAN_ROWS * N && r < n;
@@ -831,15 +834,16 @@ __global__ void __launch_bounds__(256) selective_scan_kernel(ScanArgs p) {
         cv[u] = ok ? to_f32(row[p.c_col + nn]) : 0.f;
       }
 #pragma unroll
-      for (int u = 0; u < 4; u++) {
+      for (int u = 0; u < 8; u++) {
         int i = base + lt + 128 * u;
         if (i < MIX_SCAN_ROWS * N) { b_s[i] = bv[u]; c_s[i] = cv[u]; }
       }
     }
 #pragma unroll
-    for (int u = 0; u < 4; u++) {
+    for (int u = 0; u < PER; u++) {
       int i = lt + 128 * u;
-      int r = i >> 5, ch = ch0 + (i & 31);
+      if (i >= MIX_SCAN_ROWS * CPB) continue;
+      int r = i / CPB, ch = ch0 + i % CPB;
       bool ok = r < n && ch < p.I;
       dt_s[i] = ok ? softplus_f(dtr[u]) : 0.f;
       x_s[i] = xr[u];
@@ -847,7 +851,7 @@ __global__ void __launch_bounds__(256) selective_scan_kernel(ScanArgs p) {
     }
   };
 
-  int cc = (threadIdx.x & 127) >> 2, l = threadIdx.x & 3;
+  int cc = (threadIdx.x & 127) / L, l = threadIdx.x % L;
   int ch = ch0 + cc;
   bool live = !loader && ch < p.I;
   int c = min(ch, p.I - 1);
@@ -857,7 +861,7 @@ __global__ void __launch_bounds__(256) selective_scan_kernel(ScanArgs p) {
   if (!loader) {
 #pragma unroll
     for (int i = 0; i < NPL; i++) {
-      int n = l + 4 * i;
+      int n = l + L * i;
       Areg[i] = n < N ? -expf(load_w(p.a_log, p.w_f32, (size_t)c * N + n)) : 0.f;
       S[i] = n < N ? st[n] : 0.f;
     }
@@ -871,28 +875,28 @@ __global__ void __launch_bounds__(256) selective_scan_kernel(ScanArgs p) {
       if (chunk + 1 < n_chunks) stage(chunk + 1);
     } else {
       const float* buf = sm + (size_t)(chunk & 1) * per_buf;
-      const float *dt_s = buf, *x_s = buf + MIX_SCAN_ROWS * 32, *z_s = x_s + MIX_SCAN_ROWS * 32, *b_s = z_s + MIX_SCAN_ROWS * 32,
+      const float *dt_s = buf, *x_s = buf + MIX_SCAN_ROWS * CPB, *z_s = x_s + MIX_SCAN_ROWS * CPB, *b_s = z_s + MIX_SCAN_ROWS * CPB,
                   *c_s = b_s + MIX_SCAN_ROWS * N;
       int r0 = r_begin + chunk * MIX_SCAN_ROWS;
       int n = min(MIX_SCAN_ROWS, r_end - r0);
 #pragma unroll 4
       for (int r = 0; r < n; r++) {
-        float dt = dt_s[r * 32 + cc], xv = x_s[r * 32 + cc];
+        float dt = dt_s[r * CPB + cc], xv = x_s[r * CPB + cc];
         float dx = dt * xv;
         const float* brow = b_s + r * N;
         const float* crow = c_s + r * N;
         float acc = 0.f;
 #pragma unroll
         for (int i = 0; i < NPL; i++) {
-          int nn = l + 4 * i;
+          int nn = l + L * i;
           if (nn < N) {
             S[i] = expf(dt * Areg[i]) * S[i] + dx * brow[nn];
             acc += S[i] * crow[nn];
           }
         }
-        acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-        acc += __shfl_xor_sync(0xffffffffu, acc, 2);
-        if (l == 0 && live) out[(size_t)(r0 + r) * p.ldo + ch] = from_f32<A>((acc + dsk * xv) * z_s[r * 32 + cc]);
+#pragma unroll
+        for (int o = L / 2; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+        if (l == 0 && live) out[(size_t)(r0 + r) * p.ldo + ch] = from_f32<A>((acc + dsk * xv) * z_s[r * CPB + cc]);
       }
     }
     __syncthreads();
@@ -900,7 +904,7 @@ __global__ void __launch_bounds__(256) selective_scan_kernel(ScanArgs p) {
   if (live) {
 #pragma unroll
     for (int i = 0; i < NPL; i++) {
-      int n = l + 4 * i;
+      int n = l + L * i;
       if (n < N) st[n] = S[i];
     }
   }

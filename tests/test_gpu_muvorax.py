@@ -209,8 +209,9 @@ def test_the_residual_stream_after_every_layer(folders):
 
 
 @pytest.mark.parametrize("layer", [lightning(), latent(scaling=YARN), mamba(), with_ff(lightning(1, 4, 4, (0.9,)), moe()),
-                                   with_ff(mamba(8, 2, 1, 2), dense(48)), latent(2, 4, 0, 8, 6, 1.0, dims=0)],
-                         ids=["lightning", "latent", "scan", "experts", "dense", "latent-without-rotation"])
+                                   with_ff(mamba(8, 2, 1, 2), dense(48)), latent(2, 4, 0, 8, 6, 1.0, dims=0), mamba(20, 12, 4, 3),
+                                   mamba(12, 70, 2, 2)],
+                         ids=["lightning", "latent", "scan", "experts", "dense", "latent-without-rotation", "scan-12-states", "scan-70-states"])
 def test_each_mechanism_alone(tmp_path, layer):
     cfg = config([layer], width=32, vocab=50)
     W = random_weights(cfg, 5, std=0.4)
