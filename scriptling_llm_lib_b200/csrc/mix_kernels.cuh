@@ -912,9 +912,9 @@ __global__ void __launch_bounds__(256) selective_scan_kernel(ScanArgs p) {
 
 // ------------------------------------------------------------------ routed experts
 // router: a warp per token. z [T][E] float32 are the router's logits (a product of the library, float32 sums);
-// s = sigmoid(z), choice = s + correction. Experts form n_groups equal groups of neighbours; a group's score is the sum
-// of its two largest choices; only experts of the `keep` best groups can be chosen; the `top` largest choices among
-// them are taken (ties: the lower index). Their weights are s / (sum of the chosen s + 1e-20) * scale.
+// s = sigmoid(z), c = s + correction. The experts are cut into n_groups runs of equal length, a run is rated by its best
+// two c added up, the `keep` best-rated runs stay open, and among the open experts the `top` with the highest c are picked
+// (ties: the lower index). Expert e then counts with s_e / (sum of the picked s + 1e-20) * scale.
 // idx int32 [T][top], wgt float32 [T][top].
 #define MIX_ROUTE_WARPS 4
 __global__ void __launch_bounds__(32 * MIX_ROUTE_WARPS) moe_route_kernel(const float* __restrict__ z, const void* __restrict__ corr,
@@ -926,7 +926,7 @@ __global__ void __launch_bounds__(32 * MIX_ROUTE_WARPS) moe_route_kernel(const f
   int t = blockIdx.x * MIX_ROUTE_WARPS + wid;
   if (t >= T) return;
   float* s = sm + (size_t)wid * (2 * E + n_groups);   // [E] sigmoid scores
-  float* ch = s + E;                                  // [E] choice scores (minus infinity once taken or shut out)
+  float* ch = s + E;                                  // [E] the picking scores c (-inf once picked or in a run that is shut)
   float* gs = ch + E;                                 // [n_groups]
   for (int e = lane; e < E; e += 32) {
     float sg = sigmoid_f(z[(size_t)t * E + e]);

@@ -3,13 +3,15 @@
 `act_feed_forward`: y = Wdown act(Wup x), no gate, no biases; act is the tanh form of gelu, the
 square of relu, or silu.
 
-`routed_experts`: `experts` such feed-forwards (act = relu^2 by default) of which every token uses
-`top`. Router: z = Wr x with float32 sums (one of the library's products writing float32), s = sigmoid(z); the choice is made on s + correction (a
-stored vector), the weights use s without it. Experts form `n_groups` equal groups of neighbours;
-a group's score is the sum of its two largest choice scores, and only experts of the `keep_groups`
-best groups can be chosen (the others count as minus infinity). The `top` largest choice scores
-win; their weights are s / (sum of the chosen s + 1e-20) * scale. The output is the weighted sum
-of the chosen experts' outputs.
+`routed_experts`: `experts` such feed-forwards (act = relu^2 by default); a token runs `top` of
+them. Router: z = Wr x with float32 sums (one of the library's products writing float32) and
+s = sigmoid(z). Two scores per expert follow: c = s + correction (a stored vector) decides who is
+picked, s alone decides how much a picked expert counts. The experts are cut into `n_groups` runs
+of equal length; a run is rated by its best two c added up, the `keep_groups` best-rated runs stay
+open, and every expert outside them is out of the race (its c is taken as -inf, so that a negative
+c inside an open run still beats it). Among the open experts the `top` with the highest c are picked,
+and expert e counts with s_e / (sum of the picked s + 1e-20) * scale. The output is the sum of the
+picked experts' outputs with those factors.
 
 The experts' matrices are stacked [experts, ff, hidden] and [experts, hidden, ff]. A step of few
 rows runs every (token, chosen expert) pair by itself (each streams its expert's matrices once); a

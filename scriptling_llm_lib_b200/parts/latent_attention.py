@@ -7,8 +7,8 @@ weight, are the latent c; the last rot_dim are a key part that all heads share. 
 softmax ordinary, and Wo maps the heads' outputs back. A position encoding (a rotation by a table)
 turns the rot_dim part of every query head and the shared key part; values are not turned.
 
-Only c and the rotated key part are cached: one vector of kv_rank + rot_dim per position, whatever
-the number of heads (a cache unit with one key "head" of that width and no value storage). Keys
+The cache holds c and the rotated key part and nothing else: one vector of kv_rank + rot_dim per
+position, whatever the number of heads (a cache unit with one key "head" of that width and no value storage). Keys
 and values are never formed per position. Since q_i . (Wuk_i c) = (Wuk_i^T q_i) . c, a head asks
 the cached vectors with [Wuk_i^T q_i | q_rot] directly, sums the latents with the softmax weights,
 and applies Wuv_i once to that sum. All heads of a row read the same cached rows. That is the form

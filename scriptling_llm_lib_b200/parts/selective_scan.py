@@ -1,8 +1,8 @@
 """The selective scan (the mixer of Mamba): a state vector per channel whose decay, input and
 read-out depend on the token.
 
-From the mixer's input h: Win h = [x | z], each `inner` wide. x passes a short causal convolution
-per channel with a bias, then SiLU. Wx x = [dt_low (dt_rank) | B (n_state) | C (n_state)];
+The input projection Win h gives two halves of `inner` channels, x and z. On x runs a short causal
+convolution over time, one filter and one bias per channel, followed by SiLU. Wx x = [dt_low (dt_rank) | B (n_state) | C (n_state)];
 dt = softplus(Wdt dt_low + dt_bias), one per channel; A = -exp(A_log) [inner, n_state]. Per channel c
 and state n: S[c, n] <- exp(dt_c A[c, n]) S[c, n] + dt_c x_c B_n; y_c = sum_n S[c, n] C_n + D_c x_c. The
 output is Wo (y * silu(z)).

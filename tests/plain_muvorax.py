@@ -186,9 +186,9 @@ def dense_ff(h, W, pre, rnd=ident):
 
 
 def route(h, W, pre, r):
-    """(chosen experts [T, top], weights [T, top]): sigmoid scores; the choice adds a correction per
-    expert and is limited to the groups whose two best corrected scores sum highest; the weights are
-    the uncorrected scores of the chosen, normalised, times a scale."""
+    """(picked experts [T, top], their factors [T, top]). s = sigmoid(logits); c = s + correction picks:
+    experts in runs of equal length, a run rated by its best two c, only the best-rated runs open, the
+    highest c among the open; the factors are the picked experts' s over their sum, times a scale."""
     E, top = r["experts"], r["top"]
     s = torch.sigmoid(h @ W[pre + "router"].T)
     choice = s + W[pre + "correction"]
